@@ -1,0 +1,100 @@
+/*
+ * C ABI of the B200 (sm_100a) quantized matvec / matmul library: libint4matmul_b200.so.
+ *
+ * This is the boundary a foreign-function binding attaches to.  Everything is plain pointers and
+ * sizes; all data pointers are DEVICE pointers on the current CUDA device; nothing here allocates
+ * device memory unless the entry says so; every launch goes onto the stream passed in (a
+ * cudaStream_t cast to void*, NULL = the legacy default stream the reference launches on).
+ * Calls return an i4mm_status; they never abort the process and never trap the device.
+ *
+ * Tensor contract (identical to the reference's torch extension, int4matmul.cpp:26-48):
+ *   x       fp16  (rows, N)          rows = B*M flattened, N = in-features (reduction dim)
+ *   matrix  int32 (R, S)             packed weights, S = out-features contiguous;
+ *                                    dense: R = N*bits/32; 16:32 sparse int4: R = N/16
+ *   mask    int32 (N/32, S) or NULL  16:32 keep-mask, bit l of [b, s] = keep(n = 32b+l, s)
+ *   scales  fp16  (n_groups, S)      scale >= 0: W = (q - zero) * scale, both steps rounded to fp16
+ *   zeros   fp16  (n_groups, S)      scale <  0: W = fma(+-2^(q & (2^(bits-1)-1)), -scale, zero)
+ *   out     fp16  (rows, S)
+ *   group_size  positive multiple of 64, or negative for "one group over all of N"
+ *   N, S multiples of 64.  sparse is only defined for bits == 4.
+ */
+#ifndef INT4MATMUL_B200_H
+#define INT4MATMUL_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum i4mm_status {
+    I4MM_OK = 0,
+    I4MM_ERR_BITS = 1,         /* bits not in {4, 3, 2}          (int4matmul.cpp:35, 45) */
+    I4MM_ERR_UNSUPPORTED = 2,  /* sparse with int3 / int2         (matmul.cuh:188, 331 trap in the reference) */
+    I4MM_ERR_SHAPE = 3,        /* a size rule of matmul_kernel.cu:383, 404-416 is violated */
+    I4MM_ERR_NULL = 4,         /* a required pointer is NULL */
+    I4MM_ERR_ALIGN = 5,        /* a pointer is not 16-byte aligned */
+    I4MM_ERR_WORKSPACE = 6,    /* workspace missing or smaller than i4mm_workspace_bytes() */
+    I4MM_ERR_LAUNCH = 7,       /* CUDA reported an error at launch; see i4mm_last_cuda_error() */
+    I4MM_ERR_MASK = 8,         /* a 32-block of the keep-mask does not hold exactly 16 entries */
+    I4MM_ERR_DEVICE = 9,       /* device is not sm_100 or a driver entry point is unavailable */
+    I4MM_ERR_TIMEOUT = 10      /* a bounded device-side wait gave up (status word set by the kernel) */
+} i4mm_status;
+
+/* Human-readable name of a status code. */
+const char* i4mm_status_string(int status);
+/* The cudaError_t (as int) recorded by the last call that returned I4MM_ERR_LAUNCH on this thread. */
+int i4mm_last_cuda_error(void);
+/* Library version: major*10000 + minor*100 + patch. */
+int i4mm_version(void);
+
+/*
+ * Bytes of device scratch the two multiply entries need.  The scratch holds per-CTA partial sums and
+ * the arrival counters of the split-K reduction.  It must be zero-filled once before its first use;
+ * the kernels leave the counters at zero again when they finish, so one buffer can serve every later
+ * call on the same stream.  Calls that overlap on the device must not share a buffer.
+ */
+size_t i4mm_workspace_bytes(void);
+
+/*
+ * out[r, s] (+)= sum_n x[r, n] * W16[n, s], fp32 accumulation, one rounding to fp16.
+ *
+ * Replaces matvec_packed_int<bits> / MVA_Int4_Half (matvec_kernel.cu:302-383, 198-267) and
+ * matmul_packed_int<bits> / MMA_Int4_Half (matmul_kernel.cu:375-459, 219-333).
+ *
+ *   accumulate != 0  ->  out = half(float(out) + x.W): what the reference's matvec route does to the
+ *                        caller's `outs` (matvec_kernel.cu:351, 263, 381-382)
+ *   accumulate == 0  ->  out is overwritten, as the reference's matmul route does (matmul_kernel.cu:299-332)
+ *
+ * rows = B*M may be any value >= 0 (rows == 0 returns I4MM_OK without a launch).  The entry picks the
+ * weight-streaming kernel for few rows and the tcgen05 tensor-core kernel for many; `path` forces one:
+ *   0 = automatic, 1 = streaming (mma.sync, split-K over the whole GPU), 2 = tcgen05 / TMEM pipeline.
+ */
+int i4mm_quant_matmul(int bits, int accumulate, int path,
+                      void* out, const void* matrix, const void* mask /* NULL = dense */,
+                      const void* x, const void* scales, const void* zeros,
+                      int64_t rows, int64_t N, int64_t S, int64_t n_groups, int64_t group_size,
+                      void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * 16:32 packer.  Replaces sparse_int4_pack / PackMatrix (utils_kernel.cu:67-119, 19-64).
+ *   wt_in, msk_in  uint8 (S, N): low nibble of wt_in is the weight, msk_in > 0 means keep
+ *   wt_out int32 (N/16, S), msk_out int32 (N/32, S)
+ *   violations     optional device int32; incremented once per 32-block that does not keep exactly
+ *                  16 entries (the reference device-asserts instead, utils_kernel.cu:41).  May be NULL.
+ */
+int i4mm_sparse_pack(void* wt_out, void* msk_out, const void* wt_in, const void* msk_in,
+                     int64_t S, int64_t N, void* violations, void* stream);
+
+/*
+ * Counts the 32-blocks of an already packed keep-mask (N/32, S) whose popcount is not 16 into the
+ * device int32 *violations (which the caller zeroes).  No counterpart in the reference, which trusts
+ * the mask; offered so callers can validate foreign masks without a device trap.
+ */
+int i4mm_check_mask(const void* mask, int64_t N, int64_t S, void* violations, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* INT4MATMUL_B200_H */
