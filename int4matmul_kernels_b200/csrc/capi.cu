@@ -1,0 +1,141 @@
+// extern "C" entry points of libint4matmul_b200.so: argument validation, path choice, launches.
+// The declarations and the reference interfaces they replace are in include/int4matmul_b200.h.
+#include "../../include/int4matmul_b200.h"
+
+#include "common.cuh"
+
+namespace i4mm {
+cudaError_t stream_launch(int bits, bool sparse, StreamParams p, int total_rows, int ctas, cudaStream_t stream);
+cudaError_t sparse_pack_launch(void* wt_out, void* msk_out, const void* wt_in, const void* msk_in,
+                               int S, int N, void* violations, cudaStream_t stream);
+cudaError_t check_mask_launch(const void* mask, size_t count, void* violations, cudaStream_t stream);
+int umma_launch(int bits, bool sparse, const StreamParams& p, int total_rows, int n_groups, int group_size,
+                cudaStream_t stream, cudaError_t* cuda_err);
+bool umma_supported(int bits, bool sparse, int total_rows, int N, int S);
+}  // namespace i4mm
+
+namespace {
+
+thread_local int g_last_cuda_error = 0;
+
+constexpr size_t kCounterBytes = 256 * 1024;          // 65536 column-tile counters
+constexpr int kMaxStreamCtas = 148 * 4;               // CTAs the streaming kernel is launched with
+constexpr size_t kPartialBytes = (size_t)kMaxStreamCtas * 2 * 32 * 128 * sizeof(float);
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+int fail_cuda(cudaError_t e) {
+    g_last_cuda_error = (int)e;
+    return I4MM_ERR_LAUNCH;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* i4mm_status_string(int status) {
+    switch (status) {
+        case I4MM_OK: return "ok";
+        case I4MM_ERR_BITS: return "unsupported bit width (must be 4, 3 or 2)";
+        case I4MM_ERR_UNSUPPORTED: return "unsupported combination (16:32 sparsity is defined for int4 only)";
+        case I4MM_ERR_SHAPE: return "shape rule violated";
+        case I4MM_ERR_NULL: return "required pointer is null";
+        case I4MM_ERR_ALIGN: return "pointer is not 16-byte aligned";
+        case I4MM_ERR_WORKSPACE: return "workspace missing or too small";
+        case I4MM_ERR_LAUNCH: return "CUDA launch error";
+        case I4MM_ERR_MASK: return "16:32 keep-mask violated";
+        case I4MM_ERR_DEVICE: return "device or driver not usable (needs sm_100)";
+        case I4MM_ERR_TIMEOUT: return "device-side bounded wait timed out";
+        default: return "unknown status";
+    }
+}
+
+int i4mm_last_cuda_error(void) { return g_last_cuda_error; }
+
+int i4mm_version(void) { return 100; }
+
+size_t i4mm_workspace_bytes(void) { return kCounterBytes + kPartialBytes; }
+
+int i4mm_quant_matmul(int bits, int accumulate, int path,
+                      void* out, const void* matrix, const void* mask,
+                      const void* x, const void* scales, const void* zeros,
+                      int64_t rows, int64_t N, int64_t S, int64_t n_groups, int64_t group_size,
+                      void* workspace, size_t workspace_bytes, void* stream) {
+    if (bits != 4 && bits != 3 && bits != 2) return I4MM_ERR_BITS;
+    const bool sparse = mask != nullptr;
+    if (sparse && bits != 4) return I4MM_ERR_UNSUPPORTED;
+    if (rows < 0 || N <= 0 || S <= 0 || n_groups <= 0) return I4MM_ERR_SHAPE;
+    if (N % 64 != 0 || S % 64 != 0) return I4MM_ERR_SHAPE;                 // matmul_kernel.cu:416 and the 64-row K tile
+    if (N > (1 << 30) || S > (int64_t)128 * 65536 || rows > (1 << 30)) return I4MM_ERR_SHAPE;
+    if (group_size == 0 || (group_size > 0 && group_size % 64 != 0)) return I4MM_ERR_SHAPE;   // matmul_kernel.cu:383
+    const int64_t g = group_size < 0 ? (int64_t)i4mm::kSingleGroup : group_size;           // matmul_kernel.cu:379-381
+    if (g * n_groups < N) return I4MM_ERR_SHAPE;                                               // matmul_kernel.cu:414-415
+    if (rows == 0) return I4MM_OK;
+    if (!out || !matrix || !x || !scales || !zeros) return I4MM_ERR_NULL;
+    if (!aligned16(out) || !aligned16(matrix) || !aligned16(x) || !aligned16(scales) || !aligned16(zeros) ||
+        (mask && !aligned16(mask)))
+        return I4MM_ERR_ALIGN;
+    if (path < 0 || path > 2) return I4MM_ERR_SHAPE;
+
+    i4mm::StreamParams p{};
+    p.out = (__half*)out;
+    p.matrix = (const uint32_t*)matrix;
+    p.mask = (const uint32_t*)mask;
+    p.x = (const __half*)x;
+    p.scales = (const __half*)scales;
+    p.zeros = (const __half*)zeros;
+    p.N = (int)N;
+    p.S = (int)S;
+    p.KB = (int)((N + 127) / 128);
+    p.CT = (int)((S + 127) / 128);
+    p.accumulate = accumulate ? 1 : 0;
+    const uint32_t gq = group_size < 0 ? 0u : (uint32_t)(group_size / 64);
+    p.gdiv.div = gq;
+    p.gdiv.mul = gq >= 2 ? (uint32_t)((1ull << 32) / gq + 1ull) : 0u;    // gq == 0: one group -> index 0
+
+    cudaStream_t st = (cudaStream_t)stream;
+    bool use_umma = false;
+    if (path == 2) {
+        if (!i4mm::umma_supported(bits, sparse, (int)rows, (int)N, (int)S)) return I4MM_ERR_UNSUPPORTED;
+        use_umma = true;
+    } else if (path == 0) {
+        use_umma = rows > 64 && i4mm::umma_supported(bits, sparse, (int)rows, (int)N, (int)S);
+    }
+    if (use_umma) {
+        cudaError_t ce = cudaSuccess;
+        const int rc = i4mm::umma_launch(bits, sparse, p, (int)rows, (int)n_groups, (int)(group_size < 0 ? -1 : group_size), st, &ce);
+        if (rc == I4MM_ERR_LAUNCH) return fail_cuda(ce);
+        return rc;
+    }
+
+    if (!workspace || workspace_bytes < i4mm_workspace_bytes()) return I4MM_ERR_WORKSPACE;
+    if (!aligned16(workspace)) return I4MM_ERR_ALIGN;
+    p.counters = (unsigned int*)workspace;
+    p.partials = (float*)((char*)workspace + kCounterBytes);
+    const cudaError_t e = i4mm::stream_launch(bits, sparse, p, (int)rows, kMaxStreamCtas, st);
+    if (e != cudaSuccess) return fail_cuda(e);
+    return I4MM_OK;
+}
+
+int i4mm_sparse_pack(void* wt_out, void* msk_out, const void* wt_in, const void* msk_in,
+                     int64_t S, int64_t N, void* violations, void* stream) {
+    if (S < 0 || N < 0 || N % 32 != 0 || N > (1 << 30) || S > (1 << 30)) return I4MM_ERR_SHAPE;   // utils_kernel.cu:101
+    if (S == 0 || N == 0) return I4MM_OK;
+    if (!wt_out || !msk_out || !wt_in || !msk_in) return I4MM_ERR_NULL;
+    if (!aligned16(wt_in) || !aligned16(msk_in) || !aligned16(wt_out) || !aligned16(msk_out)) return I4MM_ERR_ALIGN;
+    const cudaError_t e = i4mm::sparse_pack_launch(wt_out, msk_out, wt_in, msk_in, (int)S, (int)N, violations,
+                                                   (cudaStream_t)stream);
+    if (e != cudaSuccess) return fail_cuda(e);
+    return I4MM_OK;
+}
+
+int i4mm_check_mask(const void* mask, int64_t N, int64_t S, void* violations, void* stream) {
+    if (S < 0 || N < 0 || N % 32 != 0) return I4MM_ERR_SHAPE;
+    if (S == 0 || N == 0) return I4MM_OK;
+    if (!mask || !violations) return I4MM_ERR_NULL;
+    const cudaError_t e = i4mm::check_mask_launch(mask, (size_t)(N / 32) * (size_t)S, violations, (cudaStream_t)stream);
+    if (e != cudaSuccess) return fail_cuda(e);
+    return I4MM_OK;
+}
+
+}  // extern "C"
