@@ -1,0 +1,367 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized matmul / matvec path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl ours|reference]
+
+One step = one operator call (`quant_matmul`) over one batch of synthetic activations.  The default
+workload is the int4 dense matmul at M = 2048 on the 5120 x 20480 matrix (group 128), the configuration
+the headline TFLOP/s figure is quoted on; `--workload int4_matvec_16384` is the matvec half of the metric.
+With --gpus N (launched under torch.distributed.run, one rank per GPU) the weight matrix is column-
+sharded along S over the ranks (every rank computes its own S/N columns of the same product: total work
+fixed, "strong" scaling); there is no collective inside the timed region.
+
+Prints ONE JSON line on rank 0.  Keys beyond the basic contract:
+  roofline      dominant kernel: algorithmic flops (or bytes) per launch / CUDA-event time per launch,
+                against the measured peak in MEASURED_PEAKS.json (fallback figures if that file is absent)
+  cpu_baseline  the CPU restatement of the reference's algorithm (torch CPU dequantise + matmul, the
+                reference test's own comparator) timed on this host's cores on a bounded sample
+  e2e           the same metric through the drop-in torch extension module with HOST buffers: per step
+                one pinned host->device copy of the activations and one device->host copy of the result
+  clocks        SM clock samples taken with nvidia-smi during the timed region
+`--impl reference` times the reference's algorithm on the host CPU (the reference itself is CUDA-only and
+has no CPU implementation; its test script's torch dequantise-and-matmul comparator is what runs).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: bits, N (in), S (out), M, group, sparse
+    "int4_matmul_m2048_5120x20480": dict(bits=4, n=5120, s=20480, m=2048, g=128, sparse=False),
+    "int4_matmul_m2048_20480x5120": dict(bits=4, n=20480, s=5120, m=2048, g=128, sparse=False),
+    "int4_matvec_16384": dict(bits=4, n=16384, s=16384, m=1, g=128, sparse=False),
+    "int4_matvec_5120": dict(bits=4, n=5120, s=5120, m=1, g=128, sparse=False),
+    "int4_sparse_matvec_16384": dict(bits=4, n=16384, s=16384, m=1, g=64, sparse=True),
+    "int4_sparse_matmul_m2048_5120x20480": dict(bits=4, n=5120, s=20480, m=2048, g=64, sparse=True),
+    "int3_matvec_20480x5120": dict(bits=3, n=20480, s=5120, m=1, g=64, sparse=False),
+    "int2_matvec_20480x5120": dict(bits=2, n=20480, s=5120, m=1, g=64, sparse=False),
+    "int4_matmul_m16_20480x5120": dict(bits=4, n=20480, s=5120, m=16, g=128, sparse=False),
+    "int3_matmul_m2048_20480x5120": dict(bits=3, n=20480, s=5120, m=2048, g=64, sparse=False),
+    "int2_matmul_m2048_20480x5120": dict(bits=2, n=20480, s=5120, m=2048, g=64, sparse=False),
+}
+DEFAULT_WORKLOAD = "int4_matmul_m2048_5120x20480"
+
+# DRAM bytes per launch of the dominant kernel from ncu captures (dram__bytes_read.sum + dram__bytes_write.sum);
+# the summaries are under profiles/.  None = not captured for that workload.
+NCU_TRAFFIC_BYTES = {}
+
+L2_BYTES = 126 * 1024 * 1024
+
+
+def algorithmic_bytes(w, s_cols=None):
+    s = w["s"] if s_cols is None else s_cols
+    n, m, bits = w["n"], w["m"], w["bits"]
+    weights = (n // 16 if w["sparse"] else n * bits // 32) * s * 4
+    mask = (n // 32) * s * 4 if w["sparse"] else 0
+    groups = (n + w["g"] - 1) // w["g"]
+    return weights + mask + 2 * groups * s * 2 + m * n * 2 + m * s * 2
+
+
+def algorithmic_flops(w, s_cols=None):
+    s = w["s"] if s_cols is None else s_cols
+    return 2.0 * w["m"] * w["n"] * s
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return dict(hbm=float(d["hbm_gbs"]), tf_burst=float(d["bf16_tflops"]),
+                    tf_sustained=float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), source="measured")
+    return dict(hbm=6650.0, tf_burst=1590.0, tf_sustained=1400.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    def __init__(self, index: int):
+        self.index = index
+        self.samples = []
+        self.reasons = set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+
+    def _loop(self):
+        q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", f"--query-gpu={q}", "--format=csv,noheader,nounits", "-i", str(self.index)],
+                                     capture_output=True, text=True, timeout=5).stdout.strip().splitlines()
+                if out:
+                    f = [x.strip() for x in out[0].split(",")]
+                    self.samples.append(float(f[0]))
+                    self.max_mhz = float(f[1])
+                    for nm, v in zip(names, f[2:]):
+                        if v.lower().startswith("active"):
+                            self.reasons.add(nm)
+            except Exception:
+                pass
+            self._stop.wait(0.05)
+
+    def __enter__(self):
+        self._thread = threading.Thread(target=self._loop, daemon=True)
+        self._thread.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        self._thread.join(timeout=10)
+
+    def summary(self):
+        return dict(sm_mhz=statistics.median(self.samples) if self.samples else None, sm_max_mhz=self.max_mhz,
+                    reasons=sorted(self.reasons), samples=len(self.samples))
+
+
+def cpu_problem(w, seed=0):
+    from oracle import reference_oracle as oracle    # the CPU legs are the one place the benchmark runs oracle/
+    return oracle.make_problem(w["bits"], w["n"], w["s"], w["m"], w["g"], sparse=w["sparse"], seed=seed)
+
+
+def cpu_reference_seconds(w, problem, rows, cores):
+    """Seconds the reference's algorithm takes for ONE full step on the CPU, from a bounded sample:
+    the whole matrix is dequantised (timed in full), the matmul is timed on `rows` activation rows and
+    scaled to all M rows."""
+    from oracle import cpu_baseline
+    t_deq, t_mm = cpu_baseline.timed_pass(problem, rows, cores)
+    return t_deq + t_mm * (w["m"] / rows)
+
+
+def metric_of(w):
+    if w["m"] == 1:
+        return "int4 matvec HBM GB/s".replace("int4", f"int{w['bits']}"), "GB/s", "hbm"
+    if w["m"] <= 64:
+        return f"int{w['bits']} skinny matmul HBM GB/s", "GB/s", "hbm"
+    return f"int{w['bits']} matmul TFLOP/s (M={w['m']})", "TFLOP/s", "tensor"
+
+
+def units_per_step(w, kind, s_cols=None):
+    return algorithmic_bytes(w, s_cols) / 1e9 if kind == "hbm" else algorithmic_flops(w, s_cols) / 1e12
+
+
+def run_reference(args, w, name):
+    """--impl reference: the reference's algorithm on this host's CPU cores (see module docstring)."""
+    import torch
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    metric, unit, kind = metric_of(w)
+    p = cpu_problem(w)
+    rows = min(w["m"], 256)                     # bounded sample of the activation rows
+    times = []
+    for i in range(args.warmup + args.steps):
+        dt = cpu_reference_seconds(w, p, rows, cores)
+        if i >= args.warmup:
+            times.append(dt)
+    sec = sum(times) / len(times)
+    value = units_per_step(w, kind) / sec
+    sample = (f"per step: full {w['n']}x{w['s']} dequantise timed whole, matmul timed on {rows} of {w['m']} rows "
+              "and scaled to all rows")
+    line = dict(metric=metric, value=value, unit=unit, n_gpus=args.gpus, steps=args.steps, warmup=args.warmup,
+                ms_per_step=sec * 1e3, higher_is_better=True, scaling="strong", vs_baseline=None,
+                dtype="f16", data="synthetic", impl="reference",
+                config=dict(workload=name, **{k: w[k] for k in ("bits", "n", "s", "m", "g", "sparse")}),
+                cpu_baseline=dict(value=value, unit=unit, cores=cores, kind="port", sample=sample),
+                e2e=dict(value=value, unit=unit, h2d_bytes_per_step=0, d2h_bytes_per_step=0))
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--path", type=int, default=0, help="0 auto, 1 streaming kernel, 2 tcgen05 kernel")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="launch the timed steps directly instead of as one CUDA graph")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 0)
+    w = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        run_reference(args, w, args.workload)
+        return
+
+    import torch
+    import torch.distributed as dist
+    from int4matmul_kernels_b200 import capi, ops, packing
+    import int4matmul_kernels_b200 as pkg
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the operator has no CPU path")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    capi.load()                                   # fails loudly if the CUDA library is missing
+    ext = pkg.load_extension()
+
+    metric, unit, kind = metric_of(w)
+    s_local = w["s"] // world
+    if w["s"] % world or s_local % 64:
+        raise SystemExit("S / gpus must be a multiple of 64")
+
+    # ---- synthetic data: full matrix drawn from the seed, this rank keeps its column shard ----
+    bytes_per_step = algorithmic_bytes(w, s_local)
+    copies = max(1, -(-2 * L2_BYTES // bytes_per_step))     # rotate so that consecutive steps miss L2
+    copies = min(copies, 24)
+    layers = []
+    for c in range(copies):
+        full = packing.synthetic_weights(w["bits"], w["n"], w["s"], w["g"], sparse=w["sparse"], seed=c, device=dev)
+        layers.append({k: (packing.shard_columns(v, rank, world) if v is not None else None) for k, v in full.items()})
+        del full
+    gen = torch.Generator().manual_seed(1234)
+    x_host = torch.randn((1, w["m"], w["n"]), generator=gen).to(torch.float16).pin_memory()
+    x = x_host.to(dev)
+    outs = [torch.zeros((1, w["m"], s_local), dtype=torch.float16, device=dev) for _ in range(min(copies, 4))]
+
+    def step(i):
+        L = layers[i % copies]
+        ops.quant_matmul(w["bits"], outs[i % len(outs)], L["matrix"], x, L["scales"], L["zeros"], w["g"], L["mask"],
+                         path=args.path)
+
+    use_umma = w["m"] > 64 and args.path != 1
+    launches_per_step = 1 if use_umma else -(-w["m"] // 32)
+
+    for i in range(max(args.warmup, 3)):
+        step(i)
+    torch.cuda.synchronize()
+
+    graph = None
+    if not args.no_graph:
+        try:
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                step(0)                                   # allocates this stream's scratch outside the capture
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                for i in range(args.steps):
+                    step(i)
+            graph.replay()
+            torch.cuda.synchronize()
+        except Exception as e:                            # capture is an optimisation of the harness only
+            print(f"[bench] CUDA graph capture unavailable ({type(e).__name__}: {e}); timing direct launches", file=sys.stderr)
+            graph = None
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    with ClockSampler(local_rank) as clocks:
+        e0.record()
+        if graph is not None:
+            graph.replay()
+        else:
+            for i in range(args.steps):
+                step(i)
+        e1.record()
+        barrier()
+    ms_total = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms_total], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total = float(t.item())
+    ms_step = ms_total / args.steps
+    value = units_per_step(w, kind) / (ms_step / 1e3)          # whole job: all shards together per step
+
+    # ---- roofline of the dominant kernel (this rank's launch) ----
+    peaks = measured_peaks()
+    us_launch = ms_step * 1e3 / launches_per_step
+    if kind == "hbm":
+        achieved = algorithmic_bytes(w, s_local) / 1e9 / (ms_step / 1e3)
+        peak, runit = peaks["hbm"], "GB/s"
+    else:
+        achieved = algorithmic_flops(w, s_local) / 1e12 / (ms_step / 1e3)
+        peak, runit = peaks["tf_burst"], "TFLOP/s"
+    roofline = dict(bound=kind, achieved=achieved, peak=peak, unit=runit, frac=achieved / peak,
+                    traffic=NCU_TRAFFIC_BYTES.get(args.workload), peak_source=peaks["source"],
+                    us_per_launch=us_launch, kernel="umma" if use_umma else "stream")
+
+    # ---- end to end through the drop-in module, host buffers ----
+    e2e = None
+    if not args.no_e2e:
+        out_host = torch.empty((1, w["m"], s_local), dtype=torch.float16).pin_memory()
+        x_dev = torch.empty_like(x)
+        o_dev = torch.zeros((1, w["m"], s_local), dtype=torch.float16, device=dev)
+
+        def e2e_step(i):
+            L = layers[i % copies]
+            x_dev.copy_(x_host, non_blocking=True)
+            if w["m"] == 1:
+                o_dev.zero_()                              # the matvec route adds into outs
+            ext.quant_matmul(w["bits"], o_dev, L["matrix"], x_dev, L["scales"], L["zeros"], w["g"], L["mask"])
+            out_host.copy_(o_dev, non_blocking=True)
+
+        for i in range(3):
+            e2e_step(i)
+        barrier()
+        e0.record()
+        for i in range(args.steps):
+            e2e_step(i)
+        e1.record()
+        barrier()
+        ms_e2e = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms_e2e], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms_e2e = float(t.item())
+        e2e = dict(value=units_per_step(w, kind) / (ms_e2e / args.steps / 1e3), unit=unit,
+                   h2d_bytes_per_step=x_host.numel() * 2, d2h_bytes_per_step=out_host.numel() * 2,
+                   ms_per_step=ms_e2e / args.steps)
+
+    # ---- CPU baseline on a bounded sample (rank 0, one GPU only) ----
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        cores = os.cpu_count() or 1
+        torch.set_num_threads(cores)
+        p = cpu_problem(w)
+        rows = min(w["m"], 256)
+        cpu_reference_seconds(w, p, rows, cores)
+        reps = 3
+        sec = min(cpu_reference_seconds(w, p, rows, cores) for _ in range(reps))
+        cpu = dict(value=units_per_step(w, kind) / sec, unit=unit, cores=cores, kind="port",
+                   sample=(f"full {w['n']}x{w['s']} dequantise timed whole, matmul timed on {rows} of {w['m']} rows and "
+                           f"scaled to all rows, best of {reps}"))
+
+    if rank == 0:
+        line = dict(metric=metric, value=value, unit=unit, n_gpus=world, steps=args.steps, warmup=max(args.warmup, 3),
+                    ms_per_step=ms_step, higher_is_better=True, scaling="strong", vs_baseline=None,
+                    dtype="f16", data="synthetic",
+                    config=dict(workload=args.workload, **{k: w[k] for k in ("bits", "n", "s", "m", "g", "sparse")},
+                                sharding=f"S columns over {world} GPU(s)", l2="rotating %d weight copies (> 2x L2)" % copies,
+                                timed_as="one CUDA graph of the K steps" if graph is not None else "K direct launches"),
+                    roofline=roofline, cpu_baseline=cpu, e2e=e2e, clocks=clocks.summary(),
+                    gpu_launches=args.steps * launches_per_step)
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

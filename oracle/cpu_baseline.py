@@ -1,0 +1,48 @@
+"""The reference's algorithm on host CPU cores, with torch: the timed CPU baseline of the benchmark.
+
+TEST / MEASUREMENT INFRASTRUCTURE ONLY (see reference_oracle.py).  The reference has no CPU
+implementation; what runs here is its test script's comparator moved to the CPU: dequantise the
+whole matrix per group in fp16, W = (q - zero) * scale (kernel_test.py:138-157), then x @ W
+(kernel_test.py:248-249).  Multi-threaded through torch's intra-op pool.
+"""
+from __future__ import annotations
+
+import time
+
+import numpy as np
+import torch
+
+
+def dequantize(bits: int, q: torch.Tensor, scales: torch.Tensor, zeros: torch.Tensor, group_size: int,
+               keep: torch.Tensor | None = None) -> torch.Tensor:
+    """q uint8 (N, S), scales/zeros fp16 (n_groups, S) -> fp16 W (N, S), linear coding
+    (kernel_test.py:146-152; two fp16 roundings, as matmul.cuh:120)."""
+    n, s = q.shape
+    g = n if group_size < 0 else group_size
+    w = q.to(torch.float16).view(-1, min(g, n), s) if n % g == 0 else None
+    if w is None:
+        idx = torch.arange(n) // g
+        w16 = (q.to(torch.float16) - zeros[idx]) * scales[idx]
+    else:
+        ng = n // min(g, n)
+        w16 = ((w - zeros[:ng, None, :]) * scales[:ng, None, :]).view(n, s)
+    if keep is not None:
+        w16 = torch.where(keep, w16, torch.zeros((), dtype=torch.float16))   # exact +0 (matmul.cuh:398)
+    return w16
+
+
+def timed_pass(problem: dict, rows: int, threads: int):
+    """One dequantise + matmul pass over `rows` activation rows.  Returns (t_dequant, t_matmul) seconds."""
+    torch.set_num_threads(threads)
+    p = problem
+    q = torch.from_numpy(p["q"])
+    scales, zeros = torch.from_numpy(p["scales"]), torch.from_numpy(p["zeros"])
+    keep = torch.from_numpy(p["keep"]) if p["keep"] is not None else None
+    x = torch.from_numpy(np.ascontiguousarray(p["x"][:, :rows, :]))
+    t0 = time.perf_counter()
+    w16 = dequantize(p["bits"], q, scales, zeros, p["group_size"], keep)
+    t1 = time.perf_counter()
+    y = x @ w16
+    _ = float(y.flatten()[0])
+    t2 = time.perf_counter()
+    return t1 - t0, t2 - t1
