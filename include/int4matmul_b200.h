@@ -78,6 +78,14 @@ int i4mm_quant_matmul(int bits, int accumulate, int path,
                       void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * Waits for the stream and reports whether a kernel that used `workspace` gave up on one of its bounded
+ * device-side waits (every wait on a shared-memory barrier inside the kernels has a poll limit, after which
+ * the kernel records a status word in the workspace and returns instead of spinning).  Returns I4MM_OK, or
+ * I4MM_ERR_TIMEOUT after clearing the word.  No counterpart in the reference, whose kernels have no waits.
+ */
+int i4mm_device_status(void* workspace, void* stream);
+
+/*
  * 16:32 packer.  Replaces sparse_int4_pack / PackMatrix (utils_kernel.cu:67-119, 19-64).
  *   wt_in, msk_in  uint8 (S, N): low nibble of wt_in is the weight, msk_in > 0 means keep
  *   wt_out int32 (N/16, S), msk_out int32 (N/32, S)

@@ -7,7 +7,9 @@ from __future__ import annotations
 import ctypes
 import os
 
-_LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib", "libint4matmul_b200.so")
+# INT4MATMUL_B200_LIB points at an alternative build of the same library (e.g. one compiled with other tuning macros)
+_LIB_PATH = os.environ.get("INT4MATMUL_B200_LIB") or os.path.join(
+    os.path.dirname(os.path.abspath(__file__)), "lib", "libint4matmul_b200.so")
 _lib = None
 
 OK = 0
@@ -27,6 +29,7 @@ _SIGNATURES = {
                                          ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
                                          ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
                                          ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]),
+    "i4mm_device_status": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p]),
     "i4mm_sparse_pack": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
                                         ctypes.c_int64, ctypes.c_int64, ctypes.c_void_p, ctypes.c_void_p]),
     "i4mm_check_mask": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64, ctypes.c_void_p, ctypes.c_void_p]),

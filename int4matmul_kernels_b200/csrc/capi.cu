@@ -18,9 +18,13 @@ namespace {
 
 thread_local int g_last_cuda_error = 0;
 
-constexpr size_t kCounterBytes = 256 * 1024;          // 65536 column-tile counters
-constexpr int kMaxStreamCtas = 148 * 4;               // CTAs the streaming kernel is launched with
-constexpr size_t kPartialBytes = (size_t)kMaxStreamCtas * 2 * 32 * 128 * sizeof(float);
+constexpr size_t kCounterBytes = 256 * 1024;          // column-tile counters; the last 64 bytes hold the status word
+constexpr size_t kStatusOffset = kCounterBytes - 64;
+#ifndef I4MM_STREAM_MAXCTAS
+#define I4MM_STREAM_MAXCTAS (148 * 4)
+#endif
+constexpr int kMaxStreamCtas = I4MM_STREAM_MAXCTAS;   // upper bound on the CTAs of the streaming kernel (sizes the scratch)
+constexpr size_t kPartialBytes = (size_t)(148 * 4) * 2 * 32 * 128 * sizeof(float);
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
@@ -66,7 +70,7 @@ int i4mm_quant_matmul(int bits, int accumulate, int path,
     if (sparse && bits != 4) return I4MM_ERR_UNSUPPORTED;
     if (rows < 0 || N <= 0 || S <= 0 || n_groups <= 0) return I4MM_ERR_SHAPE;
     if (N % 64 != 0 || S % 64 != 0) return I4MM_ERR_SHAPE;                 // matmul_kernel.cu:416 and the 64-row K tile
-    if (N > (1 << 30) || S > (int64_t)128 * 65536 || rows > (1 << 30)) return I4MM_ERR_SHAPE;
+    if (N > (1 << 30) || S > (int64_t)128 * 65000 || rows > (1 << 30)) return I4MM_ERR_SHAPE;
     if (group_size == 0 || (group_size > 0 && group_size % 64 != 0)) return I4MM_ERR_SHAPE;   // matmul_kernel.cu:383
     const int64_t g = group_size < 0 ? (int64_t)i4mm::kSingleGroup : group_size;           // matmul_kernel.cu:379-381
     if (g * n_groups < N) return I4MM_ERR_SHAPE;                                               // matmul_kernel.cu:414-415
@@ -112,9 +116,23 @@ int i4mm_quant_matmul(int bits, int accumulate, int path,
     if (!aligned16(workspace)) return I4MM_ERR_ALIGN;
     p.counters = (unsigned int*)workspace;
     p.partials = (float*)((char*)workspace + kCounterBytes);
+    p.status = (int*)((char*)workspace + kStatusOffset);
     const cudaError_t e = i4mm::stream_launch(bits, sparse, p, (int)rows, kMaxStreamCtas, st);
     if (e != cudaSuccess) return fail_cuda(e);
     return I4MM_OK;
+}
+
+int i4mm_device_status(void* workspace, void* stream) {
+    if (!workspace) return I4MM_ERR_NULL;
+    int status = 0;
+    cudaError_t e = cudaMemcpyAsync(&status, (char*)workspace + kStatusOffset, sizeof(int), cudaMemcpyDeviceToHost,
+                                    (cudaStream_t)stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize((cudaStream_t)stream);
+    if (e != cudaSuccess) return fail_cuda(e);
+    if (status == 0) return I4MM_OK;
+    e = cudaMemsetAsync((char*)workspace + kStatusOffset, 0, sizeof(int), (cudaStream_t)stream);
+    if (e != cudaSuccess) return fail_cuda(e);
+    return I4MM_ERR_TIMEOUT;
 }
 
 int i4mm_sparse_pack(void* wt_out, void* msk_out, const void* wt_in, const void* msk_in,

@@ -83,6 +83,7 @@ struct StreamParams {
     const __half* zeros;     // (n_groups, S)
     float* partials;         // scratch: [2 * grid][8 * MT][128] fp32
     unsigned int* counters;  // scratch: one arrival counter per column tile, zero on entry and on exit
+    int* status;             // scratch: set non-zero by a kernel whose bounded wait gave up
     int rows;                // rows handled by this launch (<= 8 * MT)
     int N, S;
     int KB;                  // ceil(N / 128)
