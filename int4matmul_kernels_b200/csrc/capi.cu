@@ -97,13 +97,19 @@ int i4mm_quant_matmul(int bits, int accumulate, int path,
     p.gdiv.div = gq;
     p.gdiv.mul = gq >= 2 ? (uint32_t)((1ull << 32) / gq + 1ull) : 0u;    // gq == 0: one group -> index 0
 
+    if (!workspace || workspace_bytes < i4mm_workspace_bytes()) return I4MM_ERR_WORKSPACE;
+    if (!aligned16(workspace)) return I4MM_ERR_ALIGN;
+    p.counters = (unsigned int*)workspace;
+    p.partials = (float*)((char*)workspace + kCounterBytes);
+    p.status = (int*)((char*)workspace + kStatusOffset);
+
     cudaStream_t st = (cudaStream_t)stream;
     bool use_umma = false;
     if (path == 2) {
         if (!i4mm::umma_supported(bits, sparse, (int)rows, (int)N, (int)S)) return I4MM_ERR_UNSUPPORTED;
         use_umma = true;
     } else if (path == 0) {
-        use_umma = rows > 64 && i4mm::umma_supported(bits, sparse, (int)rows, (int)N, (int)S);
+        use_umma = i4mm::umma_supported(bits, sparse, (int)rows, (int)N, (int)S);
     }
     if (use_umma) {
         cudaError_t ce = cudaSuccess;
@@ -111,12 +117,6 @@ int i4mm_quant_matmul(int bits, int accumulate, int path,
         if (rc == I4MM_ERR_LAUNCH) return fail_cuda(ce);
         return rc;
     }
-
-    if (!workspace || workspace_bytes < i4mm_workspace_bytes()) return I4MM_ERR_WORKSPACE;
-    if (!aligned16(workspace)) return I4MM_ERR_ALIGN;
-    p.counters = (unsigned int*)workspace;
-    p.partials = (float*)((char*)workspace + kCounterBytes);
-    p.status = (int*)((char*)workspace + kStatusOffset);
     const cudaError_t e = i4mm::stream_launch(bits, sparse, p, (int)rows, kMaxStreamCtas, st);
     if (e != cudaSuccess) return fail_cuda(e);
     return I4MM_OK;

@@ -147,6 +147,12 @@ __device__ __forceinline__ uint4 sparse_lut_entry(int mn) {
 
 __device__ __forceinline__ uint32_t pick(const uint4& v, int c) { return c == 0 ? v.x : c == 1 ? v.y : c == 2 ? v.z : v.w; }
 
+// Row pitches inside a stage are padded so that the 8 lanes served by one shared-memory wavefront (2 quads x
+// 4 lanes, reading 16 bytes each from 4 different rows) fall into 8 different 16-byte bank groups:
+// packed rows 544 B (528 B where a lane reads rows 2t, 2t+1), mask rows 544 B, activation rows 320 B.
+constexpr int kMaskPitch = 544;
+constexpr int kXPitch = 320;
+
 template <int BITS, bool SPARSE>
 struct Format;
 
@@ -335,12 +341,6 @@ struct Format<4, true> {
         for (int p = 0; p < 16; ++p) X[p] = xr[p];
     }
 };
-
-// Row pitches inside a stage are padded so that the 8 lanes served by one shared-memory wavefront (2 quads x
-// 4 lanes, reading 16 bytes each from 4 different rows) fall into 8 different 16-byte bank groups:
-// packed rows 544 B (528 B where a lane reads rows 2t, 2t+1), mask rows 544 B, activation rows 320 B.
-constexpr int kMaskPitch = 544;
-constexpr int kXPitch = 320;
 
 // ---- stage layout ----------------------------------------------------------------------------------------
 // One stage = one k-block (128 n) of one column tile (128 columns):

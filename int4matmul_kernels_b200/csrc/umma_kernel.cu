@@ -1,6 +1,640 @@
+// Tensor-core path: tcgen05.mma with the dequantised weights as the A operand in tensor memory.
+//
+// Replaces MMA_Int4_Half (matmul_kernel.cu:219-333) and, for one or a few activation rows, MVA_Int4_Half
+// (matvec_kernel.cu:198-267).  Per CTA tile: 128 weight columns (S) on the 128 tensor-memory lanes x NT
+// activation rows on the MMA's N dimension, accumulated in fp32 in tensor memory over all of N (in-features).
+//
+//   producer warp     bulk-copies (TMA) packed weight rows + the group's scales / zeros into a shared-memory ring,
+//                     and loads the activation tile (NT rows x 64 k, 128-byte swizzle) with a tensor-map copy
+//   4 dequant warps   thread i owns weight column i: reads its packed words for 64 k from shared memory,
+//                     rebuilds fp16((q - zero) * scale) in registers, in natural k order, and writes them into its
+//                     own tensor-memory lane with tcgen05.st (one packed int32 = 8 consecutive k of one column,
+//                     which is exactly what a lane of the A operand holds)
+//   MMA warp          one thread issues 4 x tcgen05.mma (M = 128, N = NT, K = 16) per 64-k unit, A from tensor
+//                     memory, B from the swizzled shared-memory tile, and commits to mbarriers that recycle the
+//                     stages; the accumulator never leaves tensor memory until the tile is done
+//   epilogue          the dequant warps read the accumulator (tcgen05.ld), convert to fp16 and store
+//
+// For NT <= 32 the (tile, k-unit) space is cut into equal ranges per CTA (split-K over the whole GPU, partial
+// tiles summed through scratch in a fixed order); for larger NT every CTA takes whole tiles.
+// Every wait is bounded and reports through the status word instead of hanging.
 #include "../../include/int4matmul_b200.h"
+
+#include <cuda.h>
+#include <dlfcn.h>
+
 #include "common.cuh"
+#include "ptx.cuh"
+
 namespace i4mm {
-bool umma_supported(int, bool, int, int, int) { return false; }
-int umma_launch(int, bool, const StreamParams&, int, int, int, cudaStream_t, cudaError_t*) { return I4MM_ERR_UNSUPPORTED; }
+
+namespace {
+
+enum : int { MODE_FAST = 0, MODE_GENERAL = 1, MODE_SLOW = 2 };
+
+constexpr int kWStages = 6;          // packed-weight ring
+constexpr int kBStages = 4;          // activation-tile ring
+constexpr int kDequantWarps = 4;
+constexpr int kProducerWarp = 4;
+constexpr int kMmaWarp = 5;
+constexpr int kThreads = 6 * 32;
+
+struct UmmaParams {
+    __half* out;
+    const uint32_t* matrix;
+    const uint32_t* mask;
+    const __half* scales;
+    const __half* zeros;
+    float* partials;
+    unsigned int* counters;
+    int* status;
+    int rows;            // all activation rows (B * M)
+    int N, S;
+    int U;               // 64-k units per tile: N / 64
+    int CT;              // column tiles: ceil(S / 128)
+    int MTILES;          // row tiles: ceil(rows / NT)
+    int accumulate;
+    GroupDiv gdiv;
+};
+
+__device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t d;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
 }
+
+// ---- per-column constants ---------------------------------------------------------------------------------
+struct ColK {
+    uint32_t s2, z2;
+    uint32_t zb;       // sparse fast mode: the integer zero-point replicated into 4 bytes
+};
+
+// v = (1024 + q_lo * 2^a, 1024 + q_hi * 2^b) -> the two fp16 weights.  mul / base undo the two shifts exactly.
+template <int BITS, int MODE>
+__device__ __forceinline__ uint32_t finish(uint32_t v, uint32_t mul, uint32_t base, uint32_t off, const ColK& c) {
+    if (MODE == MODE_FAST) return hmul2_u(hfma2_u(v, mul, off), c.s2);         // off = base - zero
+    const uint32_t q = hfma2_u(v, mul, base);                                  // exact integers
+    if (MODE == MODE_GENERAL) return hmul2_u(hsub2_u(q, c.z2), c.s2);
+    const __half2 qh = u32_as_h2(q);
+    const __half s = __ushort_as_half((unsigned short)(c.s2 & 0xFFFFu));
+    const __half z = __ushort_as_half((unsigned short)(c.z2 & 0xFFFFu));
+    const __half lo = dequant_dynamic<BITS>(__half2uint_rz(__low2half(qh)), s, z);
+    const __half hi = dequant_dynamic<BITS>(__half2uint_rz(__high2half(qh)), s, z);
+    return h2_as_u32(__halves2half2(lo, hi));
+}
+
+// half2 constants (hi << 16 | lo)
+constexpr uint32_t MUL_1_16 = 0x2C003C00u, BASE_1_16 = 0xD400E400u;      // (x1, x16): int4 nibble pairs
+constexpr uint32_t MUL_1_4 = 0x34003C00u, BASE_1_4 = 0xDC00E400u;        // (x1, x4):  int2 crumbs 0, 1
+constexpr uint32_t MUL_16_64 = 0x24002C00u, BASE_16_64 = 0xCC00D400u;    // (x16, x64): int2 crumbs 2, 3
+constexpr uint32_t MUL_1_8 = 0x30003C00u, BASE_1_8 = 0xD800E400u;        // (x1, x8):  int3 field pairs
+constexpr uint32_t MUL_1_1 = 0x3C003C00u, BASE_1_1 = 0xE400E400u;        // sparse int4 through bytes
+
+// 16-entry table for the sparse expansion (see sparse decode): x = PRMT selector | (4 * popc) << 16, y / z = pair masks
+__device__ __forceinline__ uint4 sparse_lut_entry(int mn) {
+    uint32_t sel = 0, rank = 0, pm[2] = {0, 0};
+    for (int j = 0; j < 4; ++j) {
+        if (mn & (1 << j)) {
+            sel |= rank << (4 * j);
+            pm[j >> 1] |= 0xFFFFu << (16 * (j & 1));
+            ++rank;
+        } else {
+            sel |= 4u << (4 * j);
+        }
+    }
+    return make_uint4(sel | ((4 * rank) << 16), pm[0], pm[1], 0);
+}
+
+// ---- formats: one 64-k unit of one column -> 32 registers of fp16 pairs in natural k order -------------------
+template <int BITS, bool SPARSE>
+struct UFormat;
+
+template <>
+struct UFormat<4, false> {
+    static constexpr int WROWS = 8, MROWS = 0;       // packed rows / mask rows per 64-k unit
+    template <int MODE>
+    __device__ static __forceinline__ void decode(uint32_t wbase, uint32_t, const ColK& c, uint32_t (&A)[32], const uint4*) {
+        const uint32_t off = hsub2_u(BASE_1_16, c.z2);
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+            const uint32_t w = ptx::lds32(wbase + r * 512);
+            const uint32_t y0 = prmt(w, w, 0x1010), y1 = prmt(w, w, 0x3232);   // low / high 16 bits in both lanes
+            A[4 * r + 0] = finish<4, MODE>(and_or(y0, 0x00F0000Fu, kMagic1024), MUL_1_16, BASE_1_16, off, c);        // k0, k1
+            A[4 * r + 1] = finish<4, MODE>(and_or(y0 >> 8, 0x00F0000Fu, kMagic1024), MUL_1_16, BASE_1_16, off, c);   // k2, k3
+            A[4 * r + 2] = finish<4, MODE>(and_or(y1, 0x00F0000Fu, kMagic1024), MUL_1_16, BASE_1_16, off, c);        // k4, k5
+            A[4 * r + 3] = finish<4, MODE>(and_or(y1 >> 8, 0x00F0000Fu, kMagic1024), MUL_1_16, BASE_1_16, off, c);   // k6, k7
+        }
+    }
+};
+
+template <>
+struct UFormat<2, false> {
+    static constexpr int WROWS = 4, MROWS = 0;
+    template <int MODE>
+    __device__ static __forceinline__ void decode(uint32_t wbase, uint32_t, const ColK& c, uint32_t (&A)[32], const uint4*) {
+        const uint32_t offa = hsub2_u(BASE_1_4, c.z2), offb = hsub2_u(BASE_16_64, c.z2);
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            const uint32_t w = ptx::lds32(wbase + r * 512);
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const uint32_t y = h ? prmt(w, w, 0x3232) : prmt(w, w, 0x1010);   // crumbs 8h .. 8h+7 in both lanes
+                const uint32_t y8 = y >> 8;
+                A[8 * r + 4 * h + 0] = finish<2, MODE>(and_or(y, 0x000C0003u, kMagic1024), MUL_1_4, BASE_1_4, offa, c);
+                A[8 * r + 4 * h + 1] = finish<2, MODE>(and_or(y, 0x00C00030u, kMagic1024), MUL_16_64, BASE_16_64, offb, c);
+                A[8 * r + 4 * h + 2] = finish<2, MODE>(and_or(y8, 0x000C0003u, kMagic1024), MUL_1_4, BASE_1_4, offa, c);
+                A[8 * r + 4 * h + 3] = finish<2, MODE>(and_or(y8, 0x00C00030u, kMagic1024), MUL_16_64, BASE_16_64, offb, c);
+            }
+        }
+    }
+};
+
+template <>
+struct UFormat<3, false> {
+    static constexpr int WROWS = 6, MROWS = 0;
+    template <int MODE>
+    __device__ static __forceinline__ void decode(uint32_t wbase, uint32_t, const ColK& c, uint32_t (&A)[32], const uint4*) {
+        const uint32_t off = hsub2_u(BASE_1_8, c.z2);
+#pragma unroll
+        for (int blk = 0; blk < 2; ++blk) {
+            const uint32_t w0 = ptx::lds32(wbase + (3 * blk) * 512), w1 = ptx::lds32(wbase + (3 * blk + 1) * 512),
+                           w2 = ptx::lds32(wbase + (3 * blk + 2) * 512);
+            // the 96-bit stream in 12-bit chunks: chunk j holds fields 4j .. 4j+3 = pairs (2j, 2j+1)
+            uint32_t ch[8];
+            ch[0] = w0;
+            ch[1] = w0 >> 12;
+            ch[2] = __funnelshift_r(w0, w1, 24);
+            ch[3] = w1 >> 4;
+            ch[4] = w1 >> 16;
+            ch[5] = __funnelshift_r(w1, w2, 28);
+            ch[6] = w2 >> 8;
+            ch[7] = w2 >> 20;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const uint32_t y = prmt(ch[j], ch[j], 0x1010);
+                A[16 * blk + 2 * j + 0] = finish<3, MODE>(and_or(y, 0x00380007u, kMagic1024), MUL_1_8, BASE_1_8, off, c);
+                A[16 * blk + 2 * j + 1] = finish<3, MODE>(and_or(y >> 6, 0x00380007u, kMagic1024), MUL_1_8, BASE_1_8, off, c);
+            }
+        }
+    }
+};
+
+template <>
+struct UFormat<4, true> {
+    static constexpr int WROWS = 4, MROWS = 2;
+    template <int MODE>
+    __device__ static __forceinline__ void decode(uint32_t wbase, uint32_t mbase, const ColK& c, uint32_t (&A)[32], const uint4* lut) {
+        const uint32_t off = hsub2_u(BASE_1_1, c.z2);
+#pragma unroll
+        for (int blk = 0; blk < 2; ++blk) {
+            uint32_t lo = ptx::lds32(wbase + (2 * blk) * 512), hi = ptx::lds32(wbase + (2 * blk + 1) * 512);
+            const uint32_t m = ptx::lds32(mbase + blk * 512);
+#pragma unroll
+            for (int chn = 0; chn < 8; ++chn) {
+                const uint4 e = lut[(m >> (4 * chn)) & 0xFu];
+                uint32_t v = lo & 0xFFFFu;                       // next 4 compacted nibbles
+                v = (v | (v << 8)) & 0x00FF00FFu;
+                v = (v | (v << 4)) & 0x0F0F0F0Fu;                // one nibble per byte
+                const uint32_t dep = prmt(v, c.zb, e.x & 0xFFFFu);   // kept -> its nibble, dropped -> zero-point byte
+                uint32_t a = finish<4, MODE>(prmt(dep, 0x64646464u, 0x5140), MUL_1_1, BASE_1_1, off, c);
+                uint32_t b = finish<4, MODE>(prmt(dep, 0x64646464u, 0x7362), MUL_1_1, BASE_1_1, off, c);
+                if (MODE != MODE_FAST) { a &= e.y; b &= e.z; }   // exact zeros at dropped positions
+                A[16 * blk + 2 * chn] = a;
+                A[16 * blk + 2 * chn + 1] = b;
+                const uint32_t sh = e.x >> 16;
+                lo = __funnelshift_r(lo, hi, sh);
+                hi >>= sh;
+            }
+        }
+    }
+};
+
+template <class F>
+struct WStage {     // one stage of the packed-weight ring
+    static constexpr int kW = 0;
+    static constexpr int kMask = F::WROWS * 512;
+    static constexpr int kS = kMask + F::MROWS * 512;
+    static constexpr int kZ = kS + 256;
+    static constexpr int kBytes = kZ + 256;
+};
+
+template <int NT>
+struct Cfg {
+    static constexpr int kAStages = NT <= 32 ? 3 : 4;                 // tensor-memory stages of the A operand
+    static constexpr int kDCols = NT < 32 ? 32 : NT;
+    static constexpr int kACol0 = kDCols;
+    static constexpr int kColsUsed = kDCols + 32 * kAStages;
+    static constexpr int kTmemCols = kColsUsed <= 128 ? 128 : kColsUsed <= 256 ? 256 : 512;
+    static constexpr bool kSplit = NT <= 32;                          // split-K over CTAs with a scratch reduction
+    static constexpr int kBStageBytes = NT * 128;
+    static constexpr int kMinBlocks = NT <= 32 ? 4 : NT <= 128 ? 2 : 1;
+};
+
+struct Barriers {
+    unsigned long long w_full[kWStages], w_empty[kWStages];
+    unsigned long long b_full[kBStages], b_empty[kBStages];
+    unsigned long long a_full[4], a_empty[4];
+    unsigned long long d_full, d_empty;
+};
+
+__device__ __forceinline__ long long range_lo(long long T, long long G, long long b) { return (T * b) / G; }
+__device__ __forceinline__ int range_owner(long long T, long long G, long long t) {
+    return (int)(((t + 1) * G + T - 1) / T - 1);
+}
+
+template <int BITS, bool SPARSE, int NT>
+__global__ void __launch_bounds__(kThreads, Cfg<NT>::kMinBlocks)
+umma_kernel(const __grid_constant__ CUtensorMap tmap_x, const UmmaParams p) {
+    using F = UFormat<BITS, SPARSE>;
+    using WS = WStage<F>;
+    using C = Cfg<NT>;
+    extern __shared__ __align__(1024) unsigned char smem[];      // [B ring (1024-aligned tiles)][W ring]
+    __shared__ __align__(8) Barriers bars;
+    __shared__ uint4 lut[16];
+    __shared__ uint32_t tmem_base_smem;
+    __shared__ int s_last;
+
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t smem0 = (ptx::smem_u32(smem) + 1023u) & ~1023u;
+    const uint32_t b_ring = smem0;
+    const uint32_t w_ring = smem0 + kBStages * C::kBStageBytes;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < kWStages; ++i) {
+            ptx::mbar_init(ptx::smem_u32(&bars.w_full[i]), 1);
+            ptx::mbar_init(ptx::smem_u32(&bars.w_empty[i]), kDequantWarps);
+        }
+        for (int i = 0; i < kBStages; ++i) {
+            ptx::mbar_init(ptx::smem_u32(&bars.b_full[i]), 1);
+            ptx::mbar_init(ptx::smem_u32(&bars.b_empty[i]), 1);
+        }
+        for (int i = 0; i < 4; ++i) {
+            ptx::mbar_init(ptx::smem_u32(&bars.a_full[i]), kDequantWarps);
+            ptx::mbar_init(ptx::smem_u32(&bars.a_empty[i]), 1);
+        }
+        ptx::mbar_init(ptx::smem_u32(&bars.d_full), 1);
+        ptx::mbar_init(ptx::smem_u32(&bars.d_empty), kDequantWarps);
+        ptx::fence_mbar_init();
+    }
+    if (SPARSE && threadIdx.x < 16) lut[threadIdx.x] = sparse_lut_entry(threadIdx.x);
+    if (warp == kProducerWarp) {
+        ptx::tmem_alloc(ptx::smem_u32(&tmem_base_smem), C::kTmemCols);
+        ptx::tmem_relinquish();
+        if (lane == 0) ptx::prefetch_tmap(&tmap_x);
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::tc_fence_after_sync();
+    const uint32_t tmem_base = tmem_base_smem;
+
+    // ---- this CTA's share of the (tile, unit) space: whole tiles unless the split-K variant ----
+    const long long U = p.U;
+    const long long n_tiles = (long long)p.MTILES * p.CT;
+    const long long G = gridDim.x, b = blockIdx.x;
+    long long t_lo, t_hi;
+    if (C::kSplit) {
+        t_lo = range_lo(n_tiles * U, G, b);
+        t_hi = range_lo(n_tiles * U, G, b + 1);
+    } else {
+        t_lo = range_lo(n_tiles, G, b) * U;
+        t_hi = range_lo(n_tiles, G, b + 1) * U;
+    }
+
+    if (warp == kProducerWarp) {
+        // =========================== producer ===========================
+        uint32_t ws = 0, wph = 0, bs = 0, bph = 0;
+        for (long long t = t_lo; t < t_hi; ++t) {
+            const long long tile = t / U;
+            const int u = (int)(t - tile * U);
+            const int mt = (int)(tile / p.CT), ct = (int)(tile - (long long)mt * p.CT);
+            // packed weights + scales / zeros of this unit
+            if (!ptx::mbar_wait(ptx::smem_u32(&bars.w_empty[ws]), wph ^ 1u)) {
+                if (lane == 0) atomicExch(p.status, 11);
+                break;
+            }
+            {
+                const uint32_t st = w_ring + ws * WS::kBytes, full = ptx::smem_u32(&bars.w_full[ws]);
+                const int cols = min(128, p.S - ct * 128);
+                if (lane == 0) ptx::mbar_arrive_expect_tx(full, (uint32_t)((F::WROWS + F::MROWS) * cols * 4 + 2 * cols * 2));
+                __syncwarp();
+                const size_t S = (size_t)p.S, c0 = (size_t)ct * 128;
+                if (lane < F::WROWS)
+                    ptx::bulk_g2s(st + WS::kW + lane * 512, p.matrix + ((size_t)u * F::WROWS + lane) * S + c0, cols * 4, full);
+                else if (lane < F::WROWS + F::MROWS)
+                    ptx::bulk_g2s(st + WS::kMask + (lane - F::WROWS) * 512,
+                                  p.mask + ((size_t)u * F::MROWS + (lane - F::WROWS)) * S + c0, cols * 4, full);
+                else if (lane == 16 || lane == 17) {
+                    const size_t o = (size_t)p.gdiv((uint32_t)u) * S + c0;
+                    ptx::bulk_g2s(st + (lane == 16 ? WS::kS : WS::kZ), (lane == 16 ? p.scales : p.zeros) + o, cols * 2, full);
+                }
+            }
+            if (++ws == kWStages) { ws = 0; wph ^= 1u; }
+            // activation tile of this unit
+            if (!ptx::mbar_wait(ptx::smem_u32(&bars.b_empty[bs]), bph ^ 1u)) {
+                if (lane == 0) atomicExch(p.status, 12);
+                break;
+            }
+            if (lane == 0) {
+                const uint32_t full = ptx::smem_u32(&bars.b_full[bs]);
+                ptx::mbar_arrive_expect_tx(full, (uint32_t)C::kBStageBytes);
+                ptx::tma_load_2d(b_ring + bs * C::kBStageBytes, &tmap_x, u * 64, mt * NT, full);
+            }
+            __syncwarp();
+            if (++bs == kBStages) { bs = 0; bph ^= 1u; }
+        }
+    } else if (warp == kMmaWarp) {
+        // =========================== MMA issuer (one thread) ===========================
+        if (lane == 0) {
+            const uint32_t idesc = ptx::idesc_f16_m128(NT);
+            uint32_t as = 0, aph = 0, bs = 0, bph = 0, seg = 0;
+            bool ok = true;
+            for (long long t = t_lo; t < t_hi && ok;) {
+                const long long tile = t / U;
+                const int u0 = (int)(t - tile * U);
+                const int u1 = (int)min(U, u0 + (t_hi - t));
+                if (!ptx::mbar_wait(ptx::smem_u32(&bars.d_empty), (seg & 1u) ^ 1u)) { atomicExch(p.status, 21); ok = false; break; }
+                ptx::tc_fence_after_sync();
+                for (int u = u0; u < u1; ++u) {
+                    if (!ptx::mbar_wait(ptx::smem_u32(&bars.a_full[as]), aph) ||
+                        !ptx::mbar_wait(ptx::smem_u32(&bars.b_full[bs]), bph)) { atomicExch(p.status, 22); ok = false; break; }
+                    ptx::tc_fence_after_sync();
+                    const uint32_t bt = b_ring + bs * C::kBStageBytes;
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        ptx::umma_f16_ts(tmem_base, tmem_base + C::kACol0 + as * 32 + k * 8, ptx::smem_desc_sw128(bt + k * 32),
+                                         idesc, (u > u0 || k > 0) ? 1u : 0u);
+                    ptx::tc_commit(ptx::smem_u32(&bars.a_empty[as]));
+                    ptx::tc_commit(ptx::smem_u32(&bars.b_empty[bs]));
+                    if (++as == C::kAStages) { as = 0; aph ^= 1u; }
+                    if (++bs == kBStages) { bs = 0; bph ^= 1u; }
+                }
+                if (!ok) break;
+                ptx::tc_commit(ptx::smem_u32(&bars.d_full));
+                ++seg;
+                t += u1 - u0;
+            }
+        }
+    } else {
+        // =========================== dequant warps + epilogue ===========================
+        const int col = warp * 32 + lane;                                   // weight column in the tile = tensor-memory lane
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
+        uint32_t ws = 0, wph = 0, as = 0, aph = 0, seg = 0;
+        bool ok = true;
+        bool first_segment = true;
+        for (long long t = t_lo; t < t_hi && ok;) {
+            const long long tile = t / U;
+            const int u0 = (int)(t - tile * U);
+            const int u1 = (int)min(U, u0 + (t_hi - t));
+            const int mt = (int)(tile / p.CT), ct = (int)(tile - (long long)mt * p.CT);
+            for (int u = u0; u < u1; ++u) {
+                if (!ptx::mbar_wait(ptx::smem_u32(&bars.w_full[ws]), wph)) {
+                    if (lane == 0) atomicExch(p.status, 31);
+                    ok = false;
+                    break;
+                }
+                const uint32_t st = w_ring + ws * WS::kBytes;
+                ColK c;
+                {
+                    const uint32_t sz = ptx::lds32(st + WS::kS + (col & ~1) * 2) >> (16 * (col & 1));
+                    const uint32_t zz = ptx::lds32(st + WS::kZ + (col & ~1) * 2) >> (16 * (col & 1));
+                    c.s2 = prmt(sz, sz, 0x1010);
+                    c.z2 = prmt(zz, zz, 0x1010);
+                }
+                // fast mode needs: scale sign clear, zero-point an integer in [0, 512] ([0, 255] for the sparse format)
+                const uint32_t zr = hadd2_u(hadd2_u(c.z2, kMagic1024), H2_N1024);
+                constexpr uint32_t kAdd = SPARSE ? 0x2407u : 0x1FFFu;
+                const uint32_t zlo = c.z2 & 0xFFFFu;
+                const uint32_t not_fast = ((zlo | ((zlo & 0x7FFFu) + kAdd) | c.s2) & 0x8000u) | (zr ^ c.z2);
+                uint32_t A[32];
+                if (!__any_sync(0xFFFFFFFFu, not_fast != 0)) {
+                    if (SPARSE) c.zb = __half2uint_rz(__ushort_as_half((unsigned short)zlo)) * 0x01010101u;
+                    F::template decode<MODE_FAST>(st + WS::kW + col * 4, st + WS::kMask + col * 4, c, A, lut);
+                } else {
+                    c.zb = 0;
+                    const bool lin = __hge(__ushort_as_half((unsigned short)(c.s2 & 0xFFFFu)), __ushort_as_half(0));
+                    if (__all_sync(0xFFFFFFFFu, lin))
+                        F::template decode<MODE_GENERAL>(st + WS::kW + col * 4, st + WS::kMask + col * 4, c, A, lut);
+                    else
+                        F::template decode<MODE_SLOW>(st + WS::kW + col * 4, st + WS::kMask + col * 4, c, A, lut);
+                }
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&bars.w_empty[ws]));     // the words are in registers now
+                if (++ws == kWStages) { ws = 0; wph ^= 1u; }
+
+                if (!ptx::mbar_wait(ptx::smem_u32(&bars.a_empty[as]), aph ^ 1u)) {
+                    if (lane == 0) atomicExch(p.status, 32);
+                    ok = false;
+                    break;
+                }
+                ptx::tc_fence_after_sync();
+                ptx::tmem_st32(lane_addr + C::kACol0 + as * 32, A);
+                ptx::tc_wait_st();
+                ptx::tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&bars.a_full[as]));
+                if (++as == C::kAStages) { as = 0; aph ^= 1u; }
+            }
+            if (!ok) break;
+
+            // ---- epilogue of this segment: accumulator -> registers -> fp16 rows of `out` (or a partial tile) ----
+            if (!ptx::mbar_wait(ptx::smem_u32(&bars.d_full), seg & 1u)) {
+                if (lane == 0) atomicExch(p.status, 33);
+                ok = false;
+                break;
+            }
+            ptx::tc_fence_after_sync();
+            const bool complete = (u0 == 0) && (u1 == (int)U);
+            const int scol = ct * 128 + col;
+            const bool col_ok = scol < p.S;
+            const int row0 = mt * NT;
+            const int nrows = min(NT, p.rows - row0);
+            float* slot = nullptr;
+            if (C::kSplit && !complete) slot = p.partials + ((size_t)b * 2 + (first_segment ? 0 : 1)) * (32 * 128);
+#pragma unroll 1
+            for (int j0 = 0; j0 < NT; j0 += 16) {
+                uint32_t v[16];
+                ptx::tmem_ld16(lane_addr + j0, v);
+                ptx::tc_wait_ld();
+                if (j0 + 16 >= NT) {                       // the accumulator is free once the last chunk is in registers
+                    ptx::tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&bars.d_empty));
+                }
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const int m = j0 + j;
+                    if (m < nrows) {
+                        float f = __uint_as_float(v[j]);
+                        if (slot) {
+                            __stcg(slot + m * 128 + col, f);
+                        } else if (col_ok) {
+                            __half* o = p.out + (size_t)(row0 + m) * p.S + scol;
+                            if (p.accumulate) f += __half2float(*o);
+                            *o = __float2half_rn(f);
+                        }
+                    }
+                }
+            }
+            if (C::kSplit && !complete) {
+                const long long T = n_tiles * U;
+                __threadfence();
+                ptx::named_bar_sync(1, kDequantWarps * 32);
+                const long long lo_t = tile * U, hi_t = lo_t + U - 1;
+                const int b_lo = range_owner(T, G, lo_t), b_hi = range_owner(T, G, hi_t);
+                if (threadIdx.x == 0) {
+                    const unsigned int prev = atomicAdd(p.counters + tile, 1u);
+                    s_last = (prev == (unsigned int)(b_hi - b_lo)) ? 1 : 0;
+                }
+                ptx::named_bar_sync(1, kDequantWarps * 32);
+                if (s_last) {
+                    // the last CTA to arrive sums the partial tiles in CTA order: a fixed order, so results are reproducible
+                    __threadfence();
+                    const bool lo_starts_here = range_lo(T, G, b_lo) == lo_t;
+                    if (col_ok) {
+                        for (int m = 0; m < nrows; ++m) {
+                            float f = 0.f;
+                            for (int bb = b_lo; bb <= b_hi; ++bb) {
+                                const int which = (bb > b_lo || lo_starts_here) ? 0 : 1;
+                                f += __ldcg(p.partials + ((size_t)bb * 2 + which) * (32 * 128) + m * 128 + col);
+                            }
+                            __half* o = p.out + (size_t)(row0 + m) * p.S + scol;
+                            if (p.accumulate) f += __half2float(*o);
+                            *o = __float2half_rn(f);
+                        }
+                    }
+                    if (threadIdx.x == 0) p.counters[tile] = 0;     // leave the scratch ready for the next launch
+                }
+                ptx::named_bar_sync(1, kDequantWarps * 32);
+            }
+            ++seg;
+            t += u1 - u0;
+            first_segment = false;
+        }
+    }
+
+    // ---- teardown: every role ends up here, also after a timed-out wait ----
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::tc_fence_after_sync();
+    if (warp == kProducerWarp) ptx::tmem_dealloc(tmem_base, C::kTmemCols);
+}
+
+// ---- host side -------------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// The driver's tensor-map encoder, found at run time so that the library does not link against libcuda.
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult q = cudaDriverEntryPointSymbolNotFound;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess && ptr)
+            fn = (EncodeTiledFn)ptr;
+        if (!fn) {
+            (void)cudaGetLastError();
+            void* h = dlopen("libcuda.so.1", RTLD_NOW | RTLD_GLOBAL);
+            if (h) fn = (EncodeTiledFn)dlsym(h, "cuTensorMapEncodeTiled");
+        }
+    }
+    return fn;
+}
+
+template <int BITS, bool SPARSE, int NT>
+int launch_nt(const UmmaParams& p, const __half* x, cudaStream_t stream, cudaError_t* cuda_err) {
+    using F = UFormat<BITS, SPARSE>;
+    using C = Cfg<NT>;
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc) return I4MM_ERR_DEVICE;
+    CUtensorMap tmap;
+    const cuuint64_t dims[2] = {(cuuint64_t)p.N, (cuuint64_t)p.rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)p.N * 2};
+    const cuuint32_t box[2] = {64, (cuuint32_t)NT};
+    const cuuint32_t estr[2] = {1, 1};
+    if (enc(&tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void*)x, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return I4MM_ERR_DEVICE;
+
+    const size_t smem = 1024 + (size_t)kBStages * C::kBStageBytes + (size_t)kWStages * WStage<F>::kBytes;
+    auto kern = umma_kernel<BITS, SPARSE, NT>;
+    static int ctas_per_sm[16] = {0};
+    static int sm_count[16] = {0};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) { *cuda_err = e; return I4MM_ERR_LAUNCH; }
+    dev &= 15;
+    if (ctas_per_sm[dev] == 0) {
+        e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) { *cuda_err = e; return I4MM_ERR_LAUNCH; }
+        int n = 0, sms = 0;
+        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, kThreads, smem);
+        if (e != cudaSuccess) { *cuda_err = e; return I4MM_ERR_LAUNCH; }
+        e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (e != cudaSuccess) { *cuda_err = e; return I4MM_ERR_LAUNCH; }
+        const int tmem_limit = 512 / C::kTmemCols;          // CTAs that can hold their tensor memory at once
+        if (n > tmem_limit) n = tmem_limit;
+        sm_count[dev] = sms;
+        ctas_per_sm[dev] = n > 0 ? n : 1;
+    }
+    const long long n_tiles = (long long)p.MTILES * p.CT;
+    long long grid = (long long)sm_count[dev] * ctas_per_sm[dev];
+    const long long work = C::kSplit ? n_tiles * p.U : n_tiles;
+    if (grid > work) grid = work;
+    if (C::kSplit && grid > 148 * 4) grid = 148 * 4;        // the scratch holds two partial tiles per CTA for this many CTAs
+    kern<<<(int)grid, kThreads, smem, stream>>>(tmap, p);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) { *cuda_err = e; return I4MM_ERR_LAUNCH; }
+    return I4MM_OK;
+}
+
+template <int BITS, bool SPARSE>
+int launch_fmt(UmmaParams& p, const __half* x, cudaStream_t stream, cudaError_t* cuda_err) {
+    const int rows = p.rows;
+    const int nt = rows <= 16 ? 16 : rows <= 32 ? 32 : rows <= 64 ? 64 : rows <= 128 ? 128 : 256;
+    p.MTILES = (rows + nt - 1) / nt;
+    switch (nt) {
+        case 16: return launch_nt<BITS, SPARSE, 16>(p, x, stream, cuda_err);
+        case 32: return launch_nt<BITS, SPARSE, 32>(p, x, stream, cuda_err);
+        case 64: return launch_nt<BITS, SPARSE, 64>(p, x, stream, cuda_err);
+        case 128: return launch_nt<BITS, SPARSE, 128>(p, x, stream, cuda_err);
+        default: return launch_nt<BITS, SPARSE, 256>(p, x, stream, cuda_err);
+    }
+}
+
+}  // namespace
+
+bool umma_supported(int bits, bool sparse, int total_rows, int N, int S) {
+    (void)bits; (void)sparse; (void)S;
+    return total_rows >= 1 && N >= 64 && encode_tiled_fn() != nullptr;
+}
+
+int umma_launch(int bits, bool sparse, const StreamParams& sp, int total_rows, int n_groups, int group_size,
+                cudaStream_t stream, cudaError_t* cuda_err) {
+    (void)n_groups; (void)group_size;
+    UmmaParams p{};
+    p.out = sp.out;
+    p.matrix = sp.matrix;
+    p.mask = sp.mask;
+    p.scales = sp.scales;
+    p.zeros = sp.zeros;
+    p.partials = sp.partials;
+    p.counters = sp.counters;
+    p.status = sp.status;
+    p.rows = total_rows;
+    p.N = sp.N;
+    p.S = sp.S;
+    p.U = sp.N / 64;
+    p.CT = sp.CT;
+    p.accumulate = sp.accumulate;
+    p.gdiv = sp.gdiv;
+    if (sparse) return launch_fmt<4, true>(p, sp.x, stream, cuda_err);
+    if (bits == 4) return launch_fmt<4, false>(p, sp.x, stream, cuda_err);
+    if (bits == 3) return launch_fmt<3, false>(p, sp.x, stream, cuda_err);
+    return launch_fmt<2, false>(p, sp.x, stream, cuda_err);
+}
+
+}  // namespace i4mm
