@@ -22,6 +22,8 @@
 
 #include <cuda.h>
 #include <dlfcn.h>
+#include <cstdio>
+#include <cstdlib>
 
 #include "common.cuh"
 #include "ptx.cuh"
@@ -30,14 +32,16 @@ namespace i4mm {
 
 namespace {
 
+#ifdef I4MM_TRACE
+// debug build only: CTA 0 records clock64() stamps into the tail of the partials scratch
+#define TRACE(role, idx, slot) do { if (blockIdx.x == 0 && (idx) < 64 && lane == 0) \
+    reinterpret_cast<long long*>(p.partials + (148 * 4 * 2 * 32 * 128) - 65536)[((role) * 64 + (idx)) * 8 + (slot)] = clock64(); } while (0)
+#else
+#define TRACE(role, idx, slot) do {} while (0)
+#endif
+
 enum : int { MODE_FAST = 0, MODE_GENERAL = 1, MODE_SLOW = 2 };
 
-constexpr int kWStages = 6;          // packed-weight ring
-constexpr int kBStages = 4;          // activation-tile ring
-constexpr int kDequantWarps = 4;
-constexpr int kProducerWarp = 4;
-constexpr int kMmaWarp = 5;
-constexpr int kThreads = 6 * 32;
 
 struct UmmaParams {
     __half* out;
@@ -50,7 +54,7 @@ struct UmmaParams {
     int* status;
     int rows;            // all activation rows (B * M)
     int N, S;
-    int U;               // 64-k units per tile: N / 64
+    int U;               // 128-k units per tile: ceil(N / 128)
     int CT;              // column tiles: ceil(S / 128)
     int MTILES;          // row tiles: ceil(rows / NT)
     int accumulate;
@@ -210,17 +214,20 @@ struct UFormat<4, true> {
 };
 
 template <class F>
-struct WStage {     // one stage of the packed-weight ring
-    static constexpr int kW = 0;
-    static constexpr int kMask = F::WROWS * 512;
-    static constexpr int kS = kMask + F::MROWS * 512;
-    static constexpr int kZ = kS + 256;
-    static constexpr int kBytes = kZ + 256;
+struct WStage {     // one stage of the packed-weight ring: 128 k = two 64-k halves
+    static constexpr int kW = 0;                                 // 2 * WROWS packed rows of 512 B
+    static constexpr int kMask = 2 * F::WROWS * 512;             // 2 * MROWS mask rows of 512 B
+    static constexpr int kS = kMask + 2 * F::MROWS * 512;        // 2 rows of scales (group g0, g0 + 1), 256 B each
+    static constexpr int kZ = kS + 512;                          // 2 rows of zeros
+    static constexpr int kBytes = kZ + 512;
 };
 
 template <int NT>
 struct Cfg {
-    static constexpr int kAStages = NT <= 32 ? 3 : 4;                 // tensor-memory stages of the A operand
+    static constexpr int kWG = NT <= 32 ? 1 : 2;                      // dequant warpgroups (4 warps each)
+    static constexpr int kWarps = 4 * kWG + 3;                        // + weight producer, activation producer, MMA issuer
+    static constexpr int kThreads = kWarps * 32;
+    static constexpr int kAStages = NT <= 32 ? 3 : 4;                 // tensor-memory stages of the A operand (64 k each)
     static constexpr int kDCols = NT < 32 ? 32 : NT;
     static constexpr int kACol0 = kDCols;
     static constexpr int kColsUsed = kDCols + 32 * kAStages;
@@ -229,6 +236,9 @@ struct Cfg {
     static constexpr int kBStageBytes = NT * 128;
     static constexpr int kMinBlocks = NT <= 32 ? 4 : NT <= 128 ? 2 : 1;
 };
+
+constexpr int kWStages = 4;          // packed-weight ring (128 k per stage)
+constexpr int kBStages = 4;          // activation-tile ring (64 k per stage)
 
 struct Barriers {
     unsigned long long w_full[kWStages], w_empty[kWStages];
@@ -242,12 +252,21 @@ __device__ __forceinline__ int range_owner(long long T, long long G, long long t
     return (int)(((t + 1) * G + T - 1) / T - 1);
 }
 
+struct TensorMaps {
+    CUtensorMap x;   // fp16 (rows, N):        box 64 k x NT rows, 128-byte swizzle
+    CUtensorMap w;   // int32 (R, S):          box 128 columns x 2 * WROWS rows
+    CUtensorMap m;   // int32 (N / 32, S):     box 128 columns x 2 * MROWS rows (sparse format only)
+    CUtensorMap s;   // fp16 (n_groups, S):    box 128 columns x 2 rows
+    CUtensorMap z;
+};
+
 template <int BITS, bool SPARSE, int NT>
-__global__ void __launch_bounds__(kThreads, Cfg<NT>::kMinBlocks)
-umma_kernel(const __grid_constant__ CUtensorMap tmap_x, const UmmaParams p) {
+__global__ void __launch_bounds__(Cfg<NT>::kThreads, Cfg<NT>::kMinBlocks)
+umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
     using F = UFormat<BITS, SPARSE>;
     using WS = WStage<F>;
     using C = Cfg<NT>;
+    constexpr int kWProducer = 4 * C::kWG, kBProducer = kWProducer + 1, kMma = kWProducer + 2;
     extern __shared__ __align__(1024) unsigned char smem[];      // [B ring (1024-aligned tiles)][W ring]
     __shared__ __align__(8) Barriers bars;
     __shared__ uint4 lut[16];
@@ -262,32 +281,38 @@ umma_kernel(const __grid_constant__ CUtensorMap tmap_x, const UmmaParams p) {
     if (threadIdx.x == 0) {
         for (int i = 0; i < kWStages; ++i) {
             ptx::mbar_init(ptx::smem_u32(&bars.w_full[i]), 1);
-            ptx::mbar_init(ptx::smem_u32(&bars.w_empty[i]), kDequantWarps);
+            ptx::mbar_init(ptx::smem_u32(&bars.w_empty[i]), 4);
         }
         for (int i = 0; i < kBStages; ++i) {
             ptx::mbar_init(ptx::smem_u32(&bars.b_full[i]), 1);
             ptx::mbar_init(ptx::smem_u32(&bars.b_empty[i]), 1);
         }
         for (int i = 0; i < 4; ++i) {
-            ptx::mbar_init(ptx::smem_u32(&bars.a_full[i]), kDequantWarps);
+            ptx::mbar_init(ptx::smem_u32(&bars.a_full[i]), 4);
             ptx::mbar_init(ptx::smem_u32(&bars.a_empty[i]), 1);
         }
         ptx::mbar_init(ptx::smem_u32(&bars.d_full), 1);
-        ptx::mbar_init(ptx::smem_u32(&bars.d_empty), kDequantWarps);
+        ptx::mbar_init(ptx::smem_u32(&bars.d_empty), 4 * C::kWG);
         ptx::fence_mbar_init();
     }
     if (SPARSE && threadIdx.x < 16) lut[threadIdx.x] = sparse_lut_entry(threadIdx.x);
-    if (warp == kProducerWarp) {
+    if (warp == kWProducer) {
         ptx::tmem_alloc(ptx::smem_u32(&tmem_base_smem), C::kTmemCols);
         ptx::tmem_relinquish();
-        if (lane == 0) ptx::prefetch_tmap(&tmap_x);
+        if (lane == 0) {
+            ptx::prefetch_tmap(&tm.x);
+            ptx::prefetch_tmap(&tm.w);
+            ptx::prefetch_tmap(&tm.s);
+            ptx::prefetch_tmap(&tm.z);
+            if (SPARSE) ptx::prefetch_tmap(&tm.m);
+        }
     }
     ptx::tc_fence_before_sync();
     __syncthreads();
     ptx::tc_fence_after_sync();
     const uint32_t tmem_base = tmem_base_smem;
 
-    // ---- this CTA's share of the (tile, unit) space: whole tiles unless the split-K variant ----
+    // ---- this CTA's share of the (tile, unit) space; one unit = 128 k.  Whole tiles unless the split-K variant ----
     const long long U = p.U;
     const long long n_tiles = (long long)p.MTILES * p.CT;
     const long long G = gridDim.x, b = blockIdx.x;
@@ -300,53 +325,51 @@ umma_kernel(const __grid_constant__ CUtensorMap tmap_x, const UmmaParams p) {
         t_hi = range_lo(n_tiles, G, b + 1) * U;
     }
 
-    if (warp == kProducerWarp) {
-        // =========================== producer ===========================
-        uint32_t ws = 0, wph = 0, bs = 0, bph = 0;
-        for (long long t = t_lo; t < t_hi; ++t) {
-            const long long tile = t / U;
-            const int u = (int)(t - tile * U);
-            const int mt = (int)(tile / p.CT), ct = (int)(tile - (long long)mt * p.CT);
-            // packed weights + scales / zeros of this unit
-            if (!ptx::mbar_wait(ptx::smem_u32(&bars.w_empty[ws]), wph ^ 1u)) {
-                if (lane == 0) atomicExch(p.status, 11);
-                break;
-            }
-            {
+    if (warp == kWProducer) {
+        // =========================== packed weights + scales / zeros: one thread ===========================
+        if (lane == 0) {
+            constexpr uint32_t kBytes = (uint32_t)WS::kBytes;      // every box is copied whole (out-of-range parts are zero-filled)
+            uint32_t si = 0;
+            for (long long t = t_lo; t < t_hi; ++t, ++si) {
+                const long long tile = t / U;
+                const int u = (int)(t - tile * U);
+                const int ct = (int)(tile % p.CT);
+                const uint32_t ws = si % kWStages, wph = (si / kWStages) & 1u;
+                TRACE(0, (int)si, 0);
+                if (!ptx::mbar_wait(ptx::smem_u32(&bars.w_empty[ws]), wph ^ 1u)) { atomicExch(p.status, 11); break; }
+                TRACE(0, (int)si, 1);
                 const uint32_t st = w_ring + ws * WS::kBytes, full = ptx::smem_u32(&bars.w_full[ws]);
-                const int cols = min(128, p.S - ct * 128);
-                if (lane == 0) ptx::mbar_arrive_expect_tx(full, (uint32_t)((F::WROWS + F::MROWS) * cols * 4 + 2 * cols * 2));
-                __syncwarp();
-                const size_t S = (size_t)p.S, c0 = (size_t)ct * 128;
-                if (lane < F::WROWS)
-                    ptx::bulk_g2s(st + WS::kW + lane * 512, p.matrix + ((size_t)u * F::WROWS + lane) * S + c0, cols * 4, full);
-                else if (lane < F::WROWS + F::MROWS)
-                    ptx::bulk_g2s(st + WS::kMask + (lane - F::WROWS) * 512,
-                                  p.mask + ((size_t)u * F::MROWS + (lane - F::WROWS)) * S + c0, cols * 4, full);
-                else if (lane == 16 || lane == 17) {
-                    const size_t o = (size_t)p.gdiv((uint32_t)u) * S + c0;
-                    ptx::bulk_g2s(st + (lane == 16 ? WS::kS : WS::kZ), (lane == 16 ? p.scales : p.zeros) + o, cols * 2, full);
+                ptx::mbar_arrive_expect_tx(full, kBytes);
+                ptx::tma_load_2d(st + WS::kW, &tm.w, ct * 128, u * 2 * F::WROWS, full);
+                if (SPARSE) ptx::tma_load_2d(st + WS::kMask, &tm.m, ct * 128, u * 2 * F::MROWS, full);
+                const int g0 = (int)p.gdiv(2u * (uint32_t)u);
+                ptx::tma_load_2d(st + WS::kS, &tm.s, ct * 128, g0, full);
+                ptx::tma_load_2d(st + WS::kZ, &tm.z, ct * 128, g0, full);
+                TRACE(0, (int)si, 2);
+            }
+        }
+    } else if (warp == kBProducer) {
+        // =========================== activation tiles, 64 k at a time: one thread ===========================
+        if (lane == 0) {
+            uint32_t hi = 0;
+            for (long long t = t_lo; t < t_hi; ++t) {
+                const long long tile = t / U;
+                const int u = (int)(t - tile * U);
+                const int mt = (int)(tile / p.CT);
+                for (int h = 0; h < 2; ++h, ++hi) {
+                    const uint32_t bs = hi % kBStages, bph = (hi / kBStages) & 1u;
+                    if (!ptx::mbar_wait(ptx::smem_u32(&bars.b_empty[bs]), bph ^ 1u)) { atomicExch(p.status, 12); t = t_hi; break; }
+                    const uint32_t full = ptx::smem_u32(&bars.b_full[bs]);
+                    ptx::mbar_arrive_expect_tx(full, (uint32_t)C::kBStageBytes);
+                    ptx::tma_load_2d(b_ring + bs * C::kBStageBytes, &tm.x, u * 128 + h * 64, mt * NT, full);
                 }
             }
-            if (++ws == kWStages) { ws = 0; wph ^= 1u; }
-            // activation tile of this unit
-            if (!ptx::mbar_wait(ptx::smem_u32(&bars.b_empty[bs]), bph ^ 1u)) {
-                if (lane == 0) atomicExch(p.status, 12);
-                break;
-            }
-            if (lane == 0) {
-                const uint32_t full = ptx::smem_u32(&bars.b_full[bs]);
-                ptx::mbar_arrive_expect_tx(full, (uint32_t)C::kBStageBytes);
-                ptx::tma_load_2d(b_ring + bs * C::kBStageBytes, &tmap_x, u * 64, mt * NT, full);
-            }
-            __syncwarp();
-            if (++bs == kBStages) { bs = 0; bph ^= 1u; }
         }
-    } else if (warp == kMmaWarp) {
-        // =========================== MMA issuer (one thread) ===========================
+    } else if (warp == kMma) {
+        // =========================== MMA issuer: one thread ===========================
         if (lane == 0) {
             const uint32_t idesc = ptx::idesc_f16_m128(NT);
-            uint32_t as = 0, aph = 0, bs = 0, bph = 0, seg = 0;
+            uint32_t hi = 0, seg = 0;
             bool ok = true;
             for (long long t = t_lo; t < t_hi && ok;) {
                 const long long tile = t / U;
@@ -354,19 +377,23 @@ umma_kernel(const __grid_constant__ CUtensorMap tmap_x, const UmmaParams p) {
                 const int u1 = (int)min(U, u0 + (t_hi - t));
                 if (!ptx::mbar_wait(ptx::smem_u32(&bars.d_empty), (seg & 1u) ^ 1u)) { atomicExch(p.status, 21); ok = false; break; }
                 ptx::tc_fence_after_sync();
-                for (int u = u0; u < u1; ++u) {
-                    if (!ptx::mbar_wait(ptx::smem_u32(&bars.a_full[as]), aph) ||
-                        !ptx::mbar_wait(ptx::smem_u32(&bars.b_full[bs]), bph)) { atomicExch(p.status, 22); ok = false; break; }
+                for (int uh = 2 * u0; uh < 2 * u1; ++uh, ++hi) {
+                    const uint32_t as = hi % C::kAStages, aph = (hi / C::kAStages) & 1u;
+                    const uint32_t bs = hi % kBStages, bph = (hi / kBStages) & 1u;
+                    TRACE(1, (int)hi, 0);
+                    if (!ptx::mbar_wait(ptx::smem_u32(&bars.a_full[as]), aph)) { atomicExch(p.status, 22); ok = false; break; }
+                    TRACE(1, (int)hi, 1);
+                    if (!ptx::mbar_wait(ptx::smem_u32(&bars.b_full[bs]), bph)) { atomicExch(p.status, 23); ok = false; break; }
+                    TRACE(1, (int)hi, 2);
                     ptx::tc_fence_after_sync();
-                    const uint32_t bt = b_ring + bs * C::kBStageBytes;
+                    const uint64_t bdesc = ptx::smem_desc_sw128(b_ring + bs * C::kBStageBytes);
+                    const uint32_t a0 = tmem_base + C::kACol0 + as * 32;
 #pragma unroll
-                    for (int k = 0; k < 4; ++k)
-                        ptx::umma_f16_ts(tmem_base, tmem_base + C::kACol0 + as * 32 + k * 8, ptx::smem_desc_sw128(bt + k * 32),
-                                         idesc, (u > u0 || k > 0) ? 1u : 0u);
+                    for (int k = 0; k < 4; ++k)      // K = 16 per instruction: +8 columns of A, +32 bytes (= 2 descriptor units) of B
+                        ptx::umma_f16_ts(tmem_base, a0 + k * 8, bdesc + (uint64_t)(2 * k), idesc, (uh > 2 * u0 || k > 0) ? 1u : 0u);
                     ptx::tc_commit(ptx::smem_u32(&bars.a_empty[as]));
                     ptx::tc_commit(ptx::smem_u32(&bars.b_empty[bs]));
-                    if (++as == C::kAStages) { as = 0; aph ^= 1u; }
-                    if (++bs == kBStages) { bs = 0; bph ^= 1u; }
+                    TRACE(1, (int)hi, 3);
                 }
                 if (!ok) break;
                 ptx::tc_commit(ptx::smem_u32(&bars.d_full));
@@ -375,10 +402,11 @@ umma_kernel(const __grid_constant__ CUtensorMap tmap_x, const UmmaParams p) {
             }
         }
     } else {
-        // =========================== dequant warps + epilogue ===========================
-        const int col = warp * 32 + lane;                                   // weight column in the tile = tensor-memory lane
-        const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
-        uint32_t ws = 0, wph = 0, as = 0, aph = 0, seg = 0;
+        // =========================== dequant warpgroups + epilogue ===========================
+        const int wg = warp >> 2;                                           // warpgroup: takes every kWG-th weight stage
+        const int col = (warp & 3) * 32 + lane;                             // weight column in the tile = tensor-memory lane
+        const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
+        uint32_t si = 0, seg = 0;
         bool ok = true;
         bool first_segment = true;
         for (long long t = t_lo; t < t_hi && ok;) {
@@ -386,53 +414,66 @@ umma_kernel(const __grid_constant__ CUtensorMap tmap_x, const UmmaParams p) {
             const int u0 = (int)(t - tile * U);
             const int u1 = (int)min(U, u0 + (t_hi - t));
             const int mt = (int)(tile / p.CT), ct = (int)(tile - (long long)mt * p.CT);
-            for (int u = u0; u < u1; ++u) {
+            for (int u = u0; u < u1 && ok; ++u, ++si) {
+                if ((int)(si % C::kWG) != wg) continue;
+                const uint32_t ws = si % kWStages, wph = (si / kWStages) & 1u;
+                if (warp == 0) TRACE(2, (int)si, 0);
                 if (!ptx::mbar_wait(ptx::smem_u32(&bars.w_full[ws]), wph)) {
                     if (lane == 0) atomicExch(p.status, 31);
                     ok = false;
                     break;
                 }
+                if (warp == 0) TRACE(2, (int)si, 1);
                 const uint32_t st = w_ring + ws * WS::kBytes;
-                ColK c;
-                {
-                    const uint32_t sz = ptx::lds32(st + WS::kS + (col & ~1) * 2) >> (16 * (col & 1));
-                    const uint32_t zz = ptx::lds32(st + WS::kZ + (col & ~1) * 2) >> (16 * (col & 1));
-                    c.s2 = prmt(sz, sz, 0x1010);
-                    c.z2 = prmt(zz, zz, 0x1010);
+                const uint32_t g0 = p.gdiv(2u * (uint32_t)u);
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const uint32_t hi = 2 * si + h;
+                    const uint32_t as = hi % C::kAStages, aph = (hi / C::kAStages) & 1u;
+                    ColK c;
+                    {
+                        const uint32_t row = (h == 0) ? 0u : (p.gdiv(2u * (uint32_t)u + 1u) - g0);   // 0 or 1
+                        const uint32_t sz = ptx::lds32(st + WS::kS + row * 256 + (col & ~1) * 2) >> (16 * (col & 1));
+                        const uint32_t zz = ptx::lds32(st + WS::kZ + row * 256 + (col & ~1) * 2) >> (16 * (col & 1));
+                        c.s2 = prmt(sz, sz, 0x1010);
+                        c.z2 = prmt(zz, zz, 0x1010);
+                    }
+                    // fast mode needs: scale sign clear, zero-point an integer in [0, 512] ([0, 255] for the sparse format)
+                    const uint32_t zr = hadd2_u(hadd2_u(c.z2, kMagic1024), H2_N1024);
+                    constexpr uint32_t kAdd = SPARSE ? 0x2407u : 0x1FFFu;
+                    const uint32_t zlo = c.z2 & 0xFFFFu;
+                    const uint32_t not_fast = ((zlo | ((zlo & 0x7FFFu) + kAdd) | c.s2) & 0x8000u) | (zr ^ c.z2);
+                    const uint32_t wb = st + WS::kW + h * (F::WROWS * 512) + col * 4;
+                    const uint32_t mb = st + WS::kMask + h * (F::MROWS * 512) + col * 4;
+                    uint32_t A[32];
+                    if (!__any_sync(0xFFFFFFFFu, not_fast != 0)) {
+                        if (SPARSE) c.zb = __half2uint_rz(__ushort_as_half((unsigned short)zlo)) * 0x01010101u;
+                        F::template decode<MODE_FAST>(wb, mb, c, A, lut);
+                    } else {
+                        c.zb = 0;
+                        const bool lin = __hge(__ushort_as_half((unsigned short)(c.s2 & 0xFFFFu)), __ushort_as_half(0));
+                        if (__all_sync(0xFFFFFFFFu, lin)) F::template decode<MODE_GENERAL>(wb, mb, c, A, lut);
+                        else F::template decode<MODE_SLOW>(wb, mb, c, A, lut);
+                    }
+                    if (h == 1) {
+                        __syncwarp();
+                        if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&bars.w_empty[ws]));   // both halves are in registers now
+                    }
+                    if (warp == 0) TRACE(2, (int)si, 2 + 3 * h);
+                    if (!ptx::mbar_wait(ptx::smem_u32(&bars.a_empty[as]), aph ^ 1u)) {
+                        if (lane == 0) atomicExch(p.status, 32);
+                        ok = false;
+                        break;
+                    }
+                    if (warp == 0) TRACE(2, (int)si, 3 + 3 * h);
+                    ptx::tc_fence_after_sync();
+                    ptx::tmem_st32(lane_addr + C::kACol0 + as * 32, A);
+                    ptx::tc_wait_st();
+                    ptx::tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&bars.a_full[as]));
+                    if (warp == 0) TRACE(2, (int)si, 4 + 3 * h);
                 }
-                // fast mode needs: scale sign clear, zero-point an integer in [0, 512] ([0, 255] for the sparse format)
-                const uint32_t zr = hadd2_u(hadd2_u(c.z2, kMagic1024), H2_N1024);
-                constexpr uint32_t kAdd = SPARSE ? 0x2407u : 0x1FFFu;
-                const uint32_t zlo = c.z2 & 0xFFFFu;
-                const uint32_t not_fast = ((zlo | ((zlo & 0x7FFFu) + kAdd) | c.s2) & 0x8000u) | (zr ^ c.z2);
-                uint32_t A[32];
-                if (!__any_sync(0xFFFFFFFFu, not_fast != 0)) {
-                    if (SPARSE) c.zb = __half2uint_rz(__ushort_as_half((unsigned short)zlo)) * 0x01010101u;
-                    F::template decode<MODE_FAST>(st + WS::kW + col * 4, st + WS::kMask + col * 4, c, A, lut);
-                } else {
-                    c.zb = 0;
-                    const bool lin = __hge(__ushort_as_half((unsigned short)(c.s2 & 0xFFFFu)), __ushort_as_half(0));
-                    if (__all_sync(0xFFFFFFFFu, lin))
-                        F::template decode<MODE_GENERAL>(st + WS::kW + col * 4, st + WS::kMask + col * 4, c, A, lut);
-                    else
-                        F::template decode<MODE_SLOW>(st + WS::kW + col * 4, st + WS::kMask + col * 4, c, A, lut);
-                }
-                __syncwarp();
-                if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&bars.w_empty[ws]));     // the words are in registers now
-                if (++ws == kWStages) { ws = 0; wph ^= 1u; }
-
-                if (!ptx::mbar_wait(ptx::smem_u32(&bars.a_empty[as]), aph ^ 1u)) {
-                    if (lane == 0) atomicExch(p.status, 32);
-                    ok = false;
-                    break;
-                }
-                ptx::tc_fence_after_sync();
-                ptx::tmem_st32(lane_addr + C::kACol0 + as * 32, A);
-                ptx::tc_wait_st();
-                ptx::tc_fence_before_sync();
-                __syncwarp();
-                if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&bars.a_full[as]));
-                if (++as == C::kAStages) { as = 0; aph ^= 1u; }
             }
             if (!ok) break;
 
@@ -450,12 +491,19 @@ umma_kernel(const __grid_constant__ CUtensorMap tmap_x, const UmmaParams p) {
             const int nrows = min(NT, p.rows - row0);
             float* slot = nullptr;
             if (C::kSplit && !complete) slot = p.partials + ((size_t)b * 2 + (first_segment ? 0 : 1)) * (32 * 128);
+            constexpr int kChunks = NT / 16;                 // 16 accumulator columns at a time, dealt round-robin to the warpgroups
+            constexpr int kMyLast = ((kChunks - 1) / C::kWG) * C::kWG;   // index of the last round
+            if (wg >= kChunks) {                             // nothing to read for this warpgroup
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&bars.d_empty));
+            }
 #pragma unroll 1
-            for (int j0 = 0; j0 < NT; j0 += 16) {
+            for (int ch = wg; ch < kChunks; ch += C::kWG) {
+                const int j0 = ch * 16;
                 uint32_t v[16];
                 ptx::tmem_ld16(lane_addr + j0, v);
                 ptx::tc_wait_ld();
-                if (j0 + 16 >= NT) {                       // the accumulator is free once the last chunk is in registers
+                if (ch + C::kWG >= kChunks) {              // this warp's last chunk is in registers: its part of the accumulator is free
                     ptx::tc_fence_before_sync();
                     __syncwarp();
                     if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&bars.d_empty));
@@ -475,22 +523,23 @@ umma_kernel(const __grid_constant__ CUtensorMap tmap_x, const UmmaParams p) {
                     }
                 }
             }
+            (void)kMyLast;
             if (C::kSplit && !complete) {
                 const long long T = n_tiles * U;
                 __threadfence();
-                ptx::named_bar_sync(1, kDequantWarps * 32);
+                ptx::named_bar_sync(1, 128 * C::kWG);
                 const long long lo_t = tile * U, hi_t = lo_t + U - 1;
                 const int b_lo = range_owner(T, G, lo_t), b_hi = range_owner(T, G, hi_t);
                 if (threadIdx.x == 0) {
                     const unsigned int prev = atomicAdd(p.counters + tile, 1u);
                     s_last = (prev == (unsigned int)(b_hi - b_lo)) ? 1 : 0;
                 }
-                ptx::named_bar_sync(1, kDequantWarps * 32);
+                ptx::named_bar_sync(1, 128 * C::kWG);
                 if (s_last) {
                     // the last CTA to arrive sums the partial tiles in CTA order: a fixed order, so results are reproducible
                     __threadfence();
                     const bool lo_starts_here = range_lo(T, G, b_lo) == lo_t;
-                    if (col_ok) {
+                    if (col_ok && wg == 0) {
                         for (int m = 0; m < nrows; ++m) {
                             float f = 0.f;
                             for (int bb = b_lo; bb <= b_hi; ++bb) {
@@ -504,7 +553,7 @@ umma_kernel(const __grid_constant__ CUtensorMap tmap_x, const UmmaParams p) {
                     }
                     if (threadIdx.x == 0) p.counters[tile] = 0;     // leave the scratch ready for the next launch
                 }
-                ptx::named_bar_sync(1, kDequantWarps * 32);
+                ptx::named_bar_sync(1, 128 * C::kWG);
             }
             ++seg;
             t += u1 - u0;
@@ -516,7 +565,7 @@ umma_kernel(const __grid_constant__ CUtensorMap tmap_x, const UmmaParams p) {
     ptx::tc_fence_before_sync();
     __syncthreads();
     ptx::tc_fence_after_sync();
-    if (warp == kProducerWarp) ptx::tmem_dealloc(tmem_base, C::kTmemCols);
+    if (warp == kWProducer) ptx::tmem_dealloc(tmem_base, C::kTmemCols);
 }
 
 // ---- host side -------------------------------------------------------------------------------------------------
@@ -544,20 +593,35 @@ EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
+// 2-D row-major tensor (rows, cols) of `elem_bytes` elements, box (box_rows, box_cols)
+bool encode_2d(CUtensorMap* out, const void* base, CUtensorMapDataType dt, int elem_bytes, uint64_t rows, uint64_t cols,
+               uint32_t box_rows, uint32_t box_cols, CUtensorMapSwizzle swz) {
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc) return false;
+    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)cols * elem_bytes};
+    const cuuint32_t box[2] = {box_cols, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    return enc(out, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
+               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 template <int BITS, bool SPARSE, int NT>
-int launch_nt(const UmmaParams& p, const __half* x, cudaStream_t stream, cudaError_t* cuda_err) {
+int launch_nt(const UmmaParams& p, const __half* x, int n_groups, cudaStream_t stream, cudaError_t* cuda_err) {
     using F = UFormat<BITS, SPARSE>;
     using C = Cfg<NT>;
-    EncodeTiledFn enc = encode_tiled_fn();
-    if (!enc) return I4MM_ERR_DEVICE;
-    CUtensorMap tmap;
-    const cuuint64_t dims[2] = {(cuuint64_t)p.N, (cuuint64_t)p.rows};
-    const cuuint64_t strides[1] = {(cuuint64_t)p.N * 2};
-    const cuuint32_t box[2] = {64, (cuuint32_t)NT};
-    const cuuint32_t estr[2] = {1, 1};
-    if (enc(&tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void*)x, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-        return I4MM_ERR_DEVICE;
+    TensorMaps tm;
+    const uint64_t R = SPARSE ? (uint64_t)p.N / 16 : (uint64_t)p.N * BITS / 32;
+    bool ok = encode_2d(&tm.x, x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, p.rows, p.N, NT, 64, CU_TENSOR_MAP_SWIZZLE_128B);
+    ok = ok && encode_2d(&tm.w, p.matrix, CU_TENSOR_MAP_DATA_TYPE_INT32, 4, R, p.S, 2 * F::WROWS, 128, CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (SPARSE)
+        ok = ok && encode_2d(&tm.m, p.mask, CU_TENSOR_MAP_DATA_TYPE_INT32, 4, (uint64_t)p.N / 32, p.S, 2 * F::MROWS, 128,
+                             CU_TENSOR_MAP_SWIZZLE_NONE);
+    else
+        tm.m = tm.w;
+    ok = ok && encode_2d(&tm.s, p.scales, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, n_groups, p.S, 2, 128, CU_TENSOR_MAP_SWIZZLE_NONE);
+    ok = ok && encode_2d(&tm.z, p.zeros, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, n_groups, p.S, 2, 128, CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (!ok) return I4MM_ERR_DEVICE;
 
     const size_t smem = 1024 + (size_t)kBStages * C::kBStageBytes + (size_t)kWStages * WStage<F>::kBytes;
     auto kern = umma_kernel<BITS, SPARSE, NT>;
@@ -570,13 +634,16 @@ int launch_nt(const UmmaParams& p, const __half* x, cudaStream_t stream, cudaErr
     if (ctas_per_sm[dev] == 0) {
         e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) { *cuda_err = e; return I4MM_ERR_LAUNCH; }
-        int n = 0, sms = 0;
-        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, kThreads, smem);
-        if (e != cudaSuccess) { *cuda_err = e; return I4MM_ERR_LAUNCH; }
+        // CTAs per SM: what the launch bounds and the shared-memory budget were sized for, capped by the tensor
+        // memory (512 columns per SM).  The occupancy calculator is not used: it reports 1 for a kernel that
+        // allocates tensor memory, whatever amount the kernel asks for at run time.
+        int n = C::kMinBlocks, sms = 0;
         e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
         if (e != cudaSuccess) { *cuda_err = e; return I4MM_ERR_LAUNCH; }
-        const int tmem_limit = 512 / C::kTmemCols;          // CTAs that can hold their tensor memory at once
+        const int tmem_limit = 512 / C::kTmemCols;
         if (n > tmem_limit) n = tmem_limit;
+        const int smem_limit = (int)((227 * 1024) / (smem + 2048));
+        if (n > smem_limit) n = smem_limit;
         sm_count[dev] = sms;
         ctas_per_sm[dev] = n > 0 ? n : 1;
     }
@@ -585,23 +652,23 @@ int launch_nt(const UmmaParams& p, const __half* x, cudaStream_t stream, cudaErr
     const long long work = C::kSplit ? n_tiles * p.U : n_tiles;
     if (grid > work) grid = work;
     if (C::kSplit && grid > 148 * 4) grid = 148 * 4;        // the scratch holds two partial tiles per CTA for this many CTAs
-    kern<<<(int)grid, kThreads, smem, stream>>>(tmap, p);
+    kern<<<(int)grid, C::kThreads, smem, stream>>>(tm, p);
     e = cudaGetLastError();
     if (e != cudaSuccess) { *cuda_err = e; return I4MM_ERR_LAUNCH; }
     return I4MM_OK;
 }
 
 template <int BITS, bool SPARSE>
-int launch_fmt(UmmaParams& p, const __half* x, cudaStream_t stream, cudaError_t* cuda_err) {
+int launch_fmt(UmmaParams& p, const __half* x, int n_groups, cudaStream_t stream, cudaError_t* cuda_err) {
     const int rows = p.rows;
     const int nt = rows <= 16 ? 16 : rows <= 32 ? 32 : rows <= 64 ? 64 : rows <= 128 ? 128 : 256;
     p.MTILES = (rows + nt - 1) / nt;
     switch (nt) {
-        case 16: return launch_nt<BITS, SPARSE, 16>(p, x, stream, cuda_err);
-        case 32: return launch_nt<BITS, SPARSE, 32>(p, x, stream, cuda_err);
-        case 64: return launch_nt<BITS, SPARSE, 64>(p, x, stream, cuda_err);
-        case 128: return launch_nt<BITS, SPARSE, 128>(p, x, stream, cuda_err);
-        default: return launch_nt<BITS, SPARSE, 256>(p, x, stream, cuda_err);
+        case 16: return launch_nt<BITS, SPARSE, 16>(p, x, n_groups, stream, cuda_err);
+        case 32: return launch_nt<BITS, SPARSE, 32>(p, x, n_groups, stream, cuda_err);
+        case 64: return launch_nt<BITS, SPARSE, 64>(p, x, n_groups, stream, cuda_err);
+        case 128: return launch_nt<BITS, SPARSE, 128>(p, x, n_groups, stream, cuda_err);
+        default: return launch_nt<BITS, SPARSE, 256>(p, x, n_groups, stream, cuda_err);
     }
 }
 
@@ -614,7 +681,7 @@ bool umma_supported(int bits, bool sparse, int total_rows, int N, int S) {
 
 int umma_launch(int bits, bool sparse, const StreamParams& sp, int total_rows, int n_groups, int group_size,
                 cudaStream_t stream, cudaError_t* cuda_err) {
-    (void)n_groups; (void)group_size;
+    (void)group_size;
     UmmaParams p{};
     p.out = sp.out;
     p.matrix = sp.matrix;
@@ -627,14 +694,14 @@ int umma_launch(int bits, bool sparse, const StreamParams& sp, int total_rows, i
     p.rows = total_rows;
     p.N = sp.N;
     p.S = sp.S;
-    p.U = sp.N / 64;
+    p.U = (sp.N + 127) / 128;
     p.CT = sp.CT;
     p.accumulate = sp.accumulate;
     p.gdiv = sp.gdiv;
-    if (sparse) return launch_fmt<4, true>(p, sp.x, stream, cuda_err);
-    if (bits == 4) return launch_fmt<4, false>(p, sp.x, stream, cuda_err);
-    if (bits == 3) return launch_fmt<3, false>(p, sp.x, stream, cuda_err);
-    return launch_fmt<2, false>(p, sp.x, stream, cuda_err);
+    if (sparse) return launch_fmt<4, true>(p, sp.x, n_groups, stream, cuda_err);
+    if (bits == 4) return launch_fmt<4, false>(p, sp.x, n_groups, stream, cuda_err);
+    if (bits == 3) return launch_fmt<3, false>(p, sp.x, n_groups, stream, cuda_err);
+    return launch_fmt<2, false>(p, sp.x, n_groups, stream, cuda_err);
 }
 
 }  // namespace i4mm
