@@ -222,28 +222,28 @@ struct WStage {     // one stage of the packed-weight ring: 128 k = two 64-k hal
     static constexpr int kBytes = kZ + 512;
 };
 
+constexpr int kWStages = 3;          // packed-weight ring (128 k per stage)
+constexpr int kABStages = 3;         // ring of (A in tensor memory, activation tile in shared memory) pairs, 128 k per stage
+
 template <int NT>
 struct Cfg {
-    static constexpr int kWG = NT <= 32 ? 1 : 2;                      // dequant warpgroups (4 warps each)
+    static constexpr int kWG = 2;                                     // dequant warpgroups (4 warps each), alternating units
     static constexpr int kWarps = 4 * kWG + 3;                        // + weight producer, activation producer, MMA issuer
     static constexpr int kThreads = kWarps * 32;
-    static constexpr int kAStages = NT <= 32 ? 3 : 4;                 // tensor-memory stages of the A operand (64 k each)
-    static constexpr int kDCols = NT < 32 ? 32 : NT;
-    static constexpr int kACol0 = kDCols;
-    static constexpr int kColsUsed = kDCols + 32 * kAStages;
-    static constexpr int kTmemCols = kColsUsed <= 128 ? 128 : kColsUsed <= 256 ? 256 : 512;
+    static constexpr int kDCols = NT < 32 ? 32 : NT;                  // accumulator columns
+    static constexpr int kACol0 = kDCols;                             // A stages follow: 64 columns (128 k) each
+    static constexpr int kColsUsed = kDCols + 64 * kABStages;
+    static constexpr int kTmemCols = kColsUsed <= 256 ? 256 : 512;
     static constexpr bool kSplit = NT <= 32;                          // split-K over CTAs with a scratch reduction
-    static constexpr int kBStageBytes = NT * 128;
-    static constexpr int kMinBlocks = NT <= 32 ? 4 : NT <= 128 ? 2 : 1;
+    static constexpr int kBHalfBytes = NT * 128;                      // one 64-k activation sub-tile
+    static constexpr int kBStageBytes = 2 * kBHalfBytes;
+    static constexpr int kMinBlocks = NT <= 64 ? 2 : 1;
 };
-
-constexpr int kWStages = 4;          // packed-weight ring (128 k per stage)
-constexpr int kBStages = 4;          // activation-tile ring (64 k per stage)
 
 struct Barriers {
     unsigned long long w_full[kWStages], w_empty[kWStages];
-    unsigned long long b_full[kBStages], b_empty[kBStages];
-    unsigned long long a_full[4], a_empty[4];
+    unsigned long long ab_full[kABStages];     // 4 dequant warps + the activation producer (with its transaction bytes)
+    unsigned long long ab_free[kABStages];     // tcgen05.commit: the MMAs that read the stage are done
     unsigned long long d_full, d_empty;
 };
 
@@ -276,20 +276,16 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const uint32_t smem0 = (ptx::smem_u32(smem) + 1023u) & ~1023u;
     const uint32_t b_ring = smem0;
-    const uint32_t w_ring = smem0 + kBStages * C::kBStageBytes;
+    const uint32_t w_ring = smem0 + kABStages * C::kBStageBytes;
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < kWStages; ++i) {
             ptx::mbar_init(ptx::smem_u32(&bars.w_full[i]), 1);
             ptx::mbar_init(ptx::smem_u32(&bars.w_empty[i]), 4);
         }
-        for (int i = 0; i < kBStages; ++i) {
-            ptx::mbar_init(ptx::smem_u32(&bars.b_full[i]), 1);
-            ptx::mbar_init(ptx::smem_u32(&bars.b_empty[i]), 1);
-        }
-        for (int i = 0; i < 4; ++i) {
-            ptx::mbar_init(ptx::smem_u32(&bars.a_full[i]), 4);
-            ptx::mbar_init(ptx::smem_u32(&bars.a_empty[i]), 1);
+        for (int i = 0; i < kABStages; ++i) {
+            ptx::mbar_init(ptx::smem_u32(&bars.ab_full[i]), 4 + 1);
+            ptx::mbar_init(ptx::smem_u32(&bars.ab_free[i]), 1);
         }
         ptx::mbar_init(ptx::smem_u32(&bars.d_full), 1);
         ptx::mbar_init(ptx::smem_u32(&bars.d_empty), 4 * C::kWG);
@@ -349,27 +345,26 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
             }
         }
     } else if (warp == kBProducer) {
-        // =========================== activation tiles, 64 k at a time: one thread ===========================
+        // =========================== activation tiles, two 64-k sub-tiles per unit: one thread ===========================
         if (lane == 0) {
-            uint32_t hi = 0;
-            for (long long t = t_lo; t < t_hi; ++t) {
+            uint32_t si = 0;
+            for (long long t = t_lo; t < t_hi; ++t, ++si) {
                 const long long tile = t / U;
                 const int u = (int)(t - tile * U);
                 const int mt = (int)(tile / p.CT);
-                for (int h = 0; h < 2; ++h, ++hi) {
-                    const uint32_t bs = hi % kBStages, bph = (hi / kBStages) & 1u;
-                    if (!ptx::mbar_wait(ptx::smem_u32(&bars.b_empty[bs]), bph ^ 1u)) { atomicExch(p.status, 12); t = t_hi; break; }
-                    const uint32_t full = ptx::smem_u32(&bars.b_full[bs]);
-                    ptx::mbar_arrive_expect_tx(full, (uint32_t)C::kBStageBytes);
-                    ptx::tma_load_2d(b_ring + bs * C::kBStageBytes, &tm.x, u * 128 + h * 64, mt * NT, full);
-                }
+                const uint32_t s = si % kABStages, ph = (si / kABStages) & 1u;
+                if (!ptx::mbar_wait(ptx::smem_u32(&bars.ab_free[s]), ph ^ 1u)) { atomicExch(p.status, 12); break; }
+                const uint32_t full = ptx::smem_u32(&bars.ab_full[s]);
+                ptx::mbar_arrive_expect_tx(full, (uint32_t)C::kBStageBytes);
+                ptx::tma_load_2d(b_ring + s * C::kBStageBytes, &tm.x, u * 128, mt * NT, full);
+                ptx::tma_load_2d(b_ring + s * C::kBStageBytes + C::kBHalfBytes, &tm.x, u * 128 + 64, mt * NT, full);
             }
         }
     } else if (warp == kMma) {
         // =========================== MMA issuer: one thread ===========================
         if (lane == 0) {
             const uint32_t idesc = ptx::idesc_f16_m128(NT);
-            uint32_t hi = 0, seg = 0;
+            uint32_t si = 0, seg = 0;
             bool ok = true;
             for (long long t = t_lo; t < t_hi && ok;) {
                 const long long tile = t / U;
@@ -377,23 +372,22 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
                 const int u1 = (int)min(U, u0 + (t_hi - t));
                 if (!ptx::mbar_wait(ptx::smem_u32(&bars.d_empty), (seg & 1u) ^ 1u)) { atomicExch(p.status, 21); ok = false; break; }
                 ptx::tc_fence_after_sync();
-                for (int uh = 2 * u0; uh < 2 * u1; ++uh, ++hi) {
-                    const uint32_t as = hi % C::kAStages, aph = (hi / C::kAStages) & 1u;
-                    const uint32_t bs = hi % kBStages, bph = (hi / kBStages) & 1u;
-                    TRACE(1, (int)hi, 0);
-                    if (!ptx::mbar_wait(ptx::smem_u32(&bars.a_full[as]), aph)) { atomicExch(p.status, 22); ok = false; break; }
-                    TRACE(1, (int)hi, 1);
-                    if (!ptx::mbar_wait(ptx::smem_u32(&bars.b_full[bs]), bph)) { atomicExch(p.status, 23); ok = false; break; }
-                    TRACE(1, (int)hi, 2);
+                for (int u = u0; u < u1; ++u, ++si) {
+                    const uint32_t s = si % kABStages, ph = (si / kABStages) & 1u;
+                    TRACE(1, (int)si, 0);
+                    if (!ptx::mbar_wait(ptx::smem_u32(&bars.ab_full[s]), ph)) { atomicExch(p.status, 22); ok = false; break; }
+                    TRACE(1, (int)si, 1);
                     ptx::tc_fence_after_sync();
-                    const uint64_t bdesc = ptx::smem_desc_sw128(b_ring + bs * C::kBStageBytes);
-                    const uint32_t a0 = tmem_base + C::kACol0 + as * 32;
+                    const uint64_t bdesc = ptx::smem_desc_sw128(b_ring + s * C::kBStageBytes);
+                    const uint32_t a0 = tmem_base + C::kACol0 + s * 64;
 #pragma unroll
-                    for (int k = 0; k < 4; ++k)      // K = 16 per instruction: +8 columns of A, +32 bytes (= 2 descriptor units) of B
-                        ptx::umma_f16_ts(tmem_base, a0 + k * 8, bdesc + (uint64_t)(2 * k), idesc, (uh > 2 * u0 || k > 0) ? 1u : 0u);
-                    ptx::tc_commit(ptx::smem_u32(&bars.a_empty[as]));
-                    ptx::tc_commit(ptx::smem_u32(&bars.b_empty[bs]));
-                    TRACE(1, (int)hi, 3);
+                    for (int k = 0; k < 8; ++k) {
+                        // K = 16 per instruction: +8 columns of A; B: +32 bytes (2 descriptor units) inside a 64-k sub-tile
+                        const uint64_t bd = bdesc + (uint64_t)((k >> 2) * (C::kBHalfBytes >> 4) + (k & 3) * 2);
+                        ptx::umma_f16_ts(tmem_base, a0 + k * 8, bd, idesc, (u > u0 || k > 0) ? 1u : 0u);
+                    }
+                    ptx::tc_commit(ptx::smem_u32(&bars.ab_free[s]));
+                    TRACE(1, (int)si, 2);
                 }
                 if (!ok) break;
                 ptx::tc_commit(ptx::smem_u32(&bars.d_full));
@@ -426,10 +420,9 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
                 if (warp == 0) TRACE(2, (int)si, 1);
                 const uint32_t st = w_ring + ws * WS::kBytes;
                 const uint32_t g0 = p.gdiv(2u * (uint32_t)u);
+                const uint32_t as = si % kABStages, aph = (si / kABStages) & 1u;
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
-                    const uint32_t hi = 2 * si + h;
-                    const uint32_t as = hi % C::kAStages, aph = (hi / C::kAStages) & 1u;
                     ColK c;
                     {
                         const uint32_t row = (h == 0) ? 0u : (p.gdiv(2u * (uint32_t)u + 1u) - g0);   // 0 or 1
@@ -459,21 +452,25 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
                         __syncwarp();
                         if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&bars.w_empty[ws]));   // both halves are in registers now
                     }
-                    if (warp == 0) TRACE(2, (int)si, 2 + 3 * h);
-                    if (!ptx::mbar_wait(ptx::smem_u32(&bars.a_empty[as]), aph ^ 1u)) {
-                        if (lane == 0) atomicExch(p.status, 32);
-                        ok = false;
-                        break;
+                    if (warp == 0) TRACE(2, (int)si, 2 + 2 * h);
+                    if (h == 0) {
+                        // the A stage (and its activation tile) is free once the MMAs of its previous use have completed
+                        if (!ptx::mbar_wait(ptx::smem_u32(&bars.ab_free[as]), aph ^ 1u)) {
+                            if (lane == 0) atomicExch(p.status, 32);
+                            ok = false;
+                            break;
+                        }
+                        ptx::tc_fence_after_sync();
                     }
-                    if (warp == 0) TRACE(2, (int)si, 3 + 3 * h);
-                    ptx::tc_fence_after_sync();
-                    ptx::tmem_st32(lane_addr + C::kACol0 + as * 32, A);
-                    ptx::tc_wait_st();
-                    ptx::tc_fence_before_sync();
-                    __syncwarp();
-                    if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&bars.a_full[as]));
-                    if (warp == 0) TRACE(2, (int)si, 4 + 3 * h);
+                    if (warp == 0) TRACE(2, (int)si, 3 + 2 * h);
+                    ptx::tmem_st32(lane_addr + C::kACol0 + as * 64 + h * 32, A);
                 }
+                if (!ok) break;
+                ptx::tc_wait_st();
+                ptx::tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&bars.ab_full[as]));
+                if (warp == 0) TRACE(2, (int)si, 6);
             }
             if (!ok) break;
 
@@ -623,7 +620,7 @@ int launch_nt(const UmmaParams& p, const __half* x, int n_groups, cudaStream_t s
     ok = ok && encode_2d(&tm.z, p.zeros, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, n_groups, p.S, 2, 128, CU_TENSOR_MAP_SWIZZLE_NONE);
     if (!ok) return I4MM_ERR_DEVICE;
 
-    const size_t smem = 1024 + (size_t)kBStages * C::kBStageBytes + (size_t)kWStages * WStage<F>::kBytes;
+    const size_t smem = 1024 + (size_t)kABStages * C::kBStageBytes + (size_t)kWStages * WStage<F>::kBytes;
     auto kern = umma_kernel<BITS, SPARSE, NT>;
     static int ctas_per_sm[16] = {0};
     static int sm_count[16] = {0};
