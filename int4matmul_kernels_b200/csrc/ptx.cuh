@@ -23,18 +23,20 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
+// One poll.  The hint lets the hardware keep the thread suspended for up to that many nanoseconds while the
+// phase is incomplete (it is woken as soon as the phase completes), so waiting warps do not burn issue slots.
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        : "=r"(ok) : "r"(bar), "r"(parity), "r"(20000u) : "memory");
     return ok != 0;
 }
-// Bounded wait.  kSpinLimit polls of try_wait (each of which itself blocks for a hardware-defined time slice)
-// are seconds of wall clock: far beyond any legitimate wait here.
-constexpr uint32_t kSpinLimit = 1u << 20;
+// Bounded wait.  kSpinLimit polls of try_wait (each of which may suspend for up to ~20 us) are seconds of
+// wall clock: far beyond any legitimate wait here.
+constexpr uint32_t kSpinLimit = 1u << 18;
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
     for (uint32_t i = 0; i < kSpinLimit; ++i)
         if (mbar_try_wait(bar, parity)) return true;
