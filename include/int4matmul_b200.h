@@ -39,7 +39,8 @@ typedef enum i4mm_status {
     I4MM_ERR_LAUNCH = 7,       /* CUDA reported an error at launch; see i4mm_last_cuda_error() */
     I4MM_ERR_MASK = 8,         /* a 32-block of the keep-mask does not hold exactly 16 entries */
     I4MM_ERR_DEVICE = 9,       /* device is not sm_100 or a driver entry point is unavailable */
-    I4MM_ERR_TIMEOUT = 10      /* a bounded device-side wait gave up (status word set by the kernel) */
+    I4MM_ERR_TIMEOUT = 10,     /* a bounded device-side wait gave up (status word set by the kernel) */
+    I4MM_ERR_TOO_LARGE = 11    /* the problem exceeds the fixed scratch of i4mm_quant_matvec_static */
 } i4mm_status;
 
 /* Human-readable name of a status code. */
@@ -76,6 +77,28 @@ int i4mm_quant_matmul(int bits, int accumulate, int path,
                       const void* x, const void* scales, const void* zeros,
                       int64_t rows, int64_t N, int64_t S, int64_t n_groups, int64_t group_size,
                       void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * The same multiply as i4mm_quant_matmul on its streaming path, for callers that cannot allocate device
+ * memory (no cudaMalloc available to them: code running inside someone else's memory pool, inside a
+ * latency-critical loop where an allocation would synchronise the device, or in a sandbox that only hands out
+ * buffers registered up front).  The caller passes inputs and outputs as usual and NO workspace: the split-K
+ * scratch is a fixed 4 882 688-byte array inside the library image, held by every GPU context that loads the
+ * library until the process exits.  This entry has no counterpart in the reference.
+ *
+ *   limits   rows <= 8 and S <= 1 048 576; anything larger returns I4MM_ERR_TOO_LARGE and launches nothing
+ *   set-up   the first call on each device looks up the array's device address (cudaGetSymbolAddress) and
+ *            configures the kernel; make that first call before any stream capture begins
+ *   sharing  every call on a device uses the same array, which keeps the previous call's contents; the entry
+ *            clears the counters it needs (two small memsets on `stream`) before launching.  Two calls that
+ *            overlap on the GPU (different streams, or different host threads) race on it: serialise them.
+ *   It calls no cudaMalloc, cudaFree or any allocating library routine.  Results are identical to
+ *   i4mm_quant_matmul(path = 1) on the same inputs.
+ */
+int i4mm_quant_matvec_static(int bits, int accumulate,
+                             void* out, const void* matrix, const void* mask /* NULL = dense */,
+                             const void* x, const void* scales, const void* zeros,
+                             int64_t rows, int64_t N, int64_t S, int64_t n_groups, int64_t group_size, void* stream);
 
 /*
  * Waits for the stream and reports whether a kernel that used `workspace` gave up on one of its bounded

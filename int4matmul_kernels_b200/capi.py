@@ -14,7 +14,7 @@ _lib = None
 
 OK = 0
 ERR_BITS, ERR_UNSUPPORTED, ERR_SHAPE, ERR_NULL, ERR_ALIGN = 1, 2, 3, 4, 5
-ERR_WORKSPACE, ERR_LAUNCH, ERR_MASK, ERR_DEVICE, ERR_TIMEOUT = 6, 7, 8, 9, 10
+ERR_WORKSPACE, ERR_LAUNCH, ERR_MASK, ERR_DEVICE, ERR_TIMEOUT, ERR_TOO_LARGE = 6, 7, 8, 9, 10, 11
 
 PATH_AUTO, PATH_STREAM, PATH_TCGEN05 = 0, 1, 2
 
@@ -29,6 +29,11 @@ _SIGNATURES = {
                                          ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
                                          ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
                                          ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]),
+    "i4mm_quant_matvec_static": (ctypes.c_int, [ctypes.c_int, ctypes.c_int,
+                                                ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+                                                ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+                                                ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
+                                                ctypes.c_void_p]),
     "i4mm_device_status": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p]),
     "i4mm_sparse_pack": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
                                         ctypes.c_int64, ctypes.c_int64, ctypes.c_void_p, ctypes.c_void_p]),

@@ -50,6 +50,7 @@ const char* i4mm_status_string(int status) {
         case I4MM_ERR_MASK: return "16:32 keep-mask violated";
         case I4MM_ERR_DEVICE: return "device or driver not usable (needs sm_100)";
         case I4MM_ERR_TIMEOUT: return "device-side bounded wait timed out";
+        case I4MM_ERR_TOO_LARGE: return "problem exceeds the fixed scratch of the allocation-free entry (rows <= 8, S <= 1048576)";
         default: return "unknown status";
     }
 }
