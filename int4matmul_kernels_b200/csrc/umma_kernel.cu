@@ -228,7 +228,8 @@ constexpr int kABStages = 3;         // ring of (A in tensor memory, activation 
 template <int NT>
 struct Cfg {
     static constexpr int kWG = 2;                                     // dequant warpgroups (4 warps each), alternating units
-    static constexpr int kWarps = 4 * kWG + 3;                        // + weight producer, activation producer, MMA issuer
+    static constexpr bool kEpiWarps = NT >= 128;                      // a warpgroup of its own for the epilogue (else dequant warpgroup 0 does it)
+    static constexpr int kWarps = 4 * kWG + (kEpiWarps ? 4 : 0) + 3;  // + weight producer, activation producer, MMA issuer
     static constexpr int kThreads = kWarps * 32;
     static constexpr int kDCols = NT < 32 ? 32 : NT;                  // accumulator columns
     static constexpr int kACol0 = kDCols;                             // A stages follow: 64 columns (128 k) each
@@ -266,7 +267,8 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
     using F = UFormat<BITS, SPARSE>;
     using WS = WStage<F>;
     using C = Cfg<NT>;
-    constexpr int kWProducer = 4 * C::kWG, kBProducer = kWProducer + 1, kMma = kWProducer + 2;
+    constexpr int kEpiWarp0 = 4 * C::kWG;                           // first epilogue warp (a multiple of 4: lane quarter = warp % 4)
+    constexpr int kWProducer = kEpiWarp0 + (C::kEpiWarps ? 4 : 0), kBProducer = kWProducer + 1, kMma = kWProducer + 2;
     extern __shared__ __align__(1024) unsigned char smem[];      // [B ring (1024-aligned tiles)][W ring]
     __shared__ __align__(8) Barriers bars;
     __shared__ uint4 lut[16];
@@ -277,6 +279,7 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
     const uint32_t smem0 = (ptx::smem_u32(smem) + 1023u) & ~1023u;
     const uint32_t b_ring = smem0;
     const uint32_t w_ring = smem0 + kABStages * C::kBStageBytes;
+    const uint32_t epi_tile = w_ring + kWStages * WS::kBytes;     // 4 KB transposition tile of the epilogue warps (NT >= 128)
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < kWStages; ++i) {
@@ -288,7 +291,7 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
             ptx::mbar_init(ptx::smem_u32(&bars.ab_free[i]), 1);
         }
         ptx::mbar_init(ptx::smem_u32(&bars.d_full), 1);
-        ptx::mbar_init(ptx::smem_u32(&bars.d_empty), 4 * C::kWG);
+        ptx::mbar_init(ptx::smem_u32(&bars.d_empty), 4);
         ptx::fence_mbar_init();
     }
     if (SPARSE && threadIdx.x < 16) lut[threadIdx.x] = sparse_lut_entry(threadIdx.x);
@@ -370,7 +373,9 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
                 const long long tile = t / U;
                 const int u0 = (int)(t - tile * U);
                 const int u1 = (int)min(U, u0 + (t_hi - t));
+                TRACE(3, (int)seg, 4);
                 if (!ptx::mbar_wait(ptx::smem_u32(&bars.d_empty), (seg & 1u) ^ 1u)) { atomicExch(p.status, 21); ok = false; break; }
+                TRACE(3, (int)seg, 5);
                 ptx::tc_fence_after_sync();
                 for (int u = u0; u < u1; ++u, ++si) {
                     const uint32_t s = si % kABStages, ph = (si / kABStages) & 1u;
@@ -391,96 +396,26 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
                 }
                 if (!ok) break;
                 ptx::tc_commit(ptx::smem_u32(&bars.d_full));
+                TRACE(3, (int)seg, 6);
                 ++seg;
                 t += u1 - u0;
             }
         }
     } else {
-        // =========================== dequant warpgroups + epilogue ===========================
-        const int wg = warp >> 2;                                           // warpgroup: takes every kWG-th weight stage
-        const int col = (warp & 3) * 32 + lane;                             // weight column in the tile = tensor-memory lane
-        const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
-        uint32_t si = 0, seg = 0;
-        bool ok = true;
-        bool first_segment = true;
-        for (long long t = t_lo; t < t_hi && ok;) {
-            const long long tile = t / U;
-            const int u0 = (int)(t - tile * U);
-            const int u1 = (int)min(U, u0 + (t_hi - t));
+        // =========================== dequant warpgroups; epilogue warps ===========================
+        // Accumulator of one finished segment -> fp16 rows of `out`, or a partial tile for the split-K reduction.
+        // Run by 4 warps whose index modulo 4 selects the 32 tensor-memory lanes (= weight columns) they may read.
+        auto epilogue = [&](uint32_t seg, long long tile, int u0, int u1, bool first_segment) -> bool {
             const int mt = (int)(tile / p.CT), ct = (int)(tile - (long long)mt * p.CT);
-            for (int u = u0; u < u1 && ok; ++u, ++si) {
-                if ((int)(si % C::kWG) != wg) continue;
-                const uint32_t ws = si % kWStages, wph = (si / kWStages) & 1u;
-                if (warp == 0) TRACE(2, (int)si, 0);
-                if (!ptx::mbar_wait(ptx::smem_u32(&bars.w_full[ws]), wph)) {
-                    if (lane == 0) atomicExch(p.status, 31);
-                    ok = false;
-                    break;
-                }
-                if (warp == 0) TRACE(2, (int)si, 1);
-                const uint32_t st = w_ring + ws * WS::kBytes;
-                const uint32_t g0 = p.gdiv(2u * (uint32_t)u);
-                const uint32_t as = si % kABStages, aph = (si / kABStages) & 1u;
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    ColK c;
-                    {
-                        const uint32_t row = (h == 0) ? 0u : (p.gdiv(2u * (uint32_t)u + 1u) - g0);   // 0 or 1
-                        const uint32_t sz = ptx::lds32(st + WS::kS + row * 256 + (col & ~1) * 2) >> (16 * (col & 1));
-                        const uint32_t zz = ptx::lds32(st + WS::kZ + row * 256 + (col & ~1) * 2) >> (16 * (col & 1));
-                        c.s2 = prmt(sz, sz, 0x1010);
-                        c.z2 = prmt(zz, zz, 0x1010);
-                    }
-                    // fast mode needs: scale sign clear, zero-point an integer in [0, 512] ([0, 255] for the sparse format)
-                    const uint32_t zr = hadd2_u(hadd2_u(c.z2, kMagic1024), H2_N1024);
-                    constexpr uint32_t kAdd = SPARSE ? 0x2407u : 0x1FFFu;
-                    const uint32_t zlo = c.z2 & 0xFFFFu;
-                    const uint32_t not_fast = ((zlo | ((zlo & 0x7FFFu) + kAdd) | c.s2) & 0x8000u) | (zr ^ c.z2);
-                    const uint32_t wb = st + WS::kW + h * (F::WROWS * 512) + col * 4;
-                    const uint32_t mb = st + WS::kMask + h * (F::MROWS * 512) + col * 4;
-                    uint32_t A[32];
-                    if (!__any_sync(0xFFFFFFFFu, not_fast != 0)) {
-                        if (SPARSE) c.zb = __half2uint_rz(__ushort_as_half((unsigned short)zlo)) * 0x01010101u;
-                        F::template decode<MODE_FAST>(wb, mb, c, A, lut);
-                    } else {
-                        c.zb = 0;
-                        const bool lin = __hge(__ushort_as_half((unsigned short)(c.s2 & 0xFFFFu)), __ushort_as_half(0));
-                        if (__all_sync(0xFFFFFFFFu, lin)) F::template decode<MODE_GENERAL>(wb, mb, c, A, lut);
-                        else F::template decode<MODE_SLOW>(wb, mb, c, A, lut);
-                    }
-                    if (h == 1) {
-                        __syncwarp();
-                        if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&bars.w_empty[ws]));   // both halves are in registers now
-                    }
-                    if (warp == 0) TRACE(2, (int)si, 2 + 2 * h);
-                    if (h == 0) {
-                        // the A stage (and its activation tile) is free once the MMAs of its previous use have completed
-                        if (!ptx::mbar_wait(ptx::smem_u32(&bars.ab_free[as]), aph ^ 1u)) {
-                            if (lane == 0) atomicExch(p.status, 32);
-                            ok = false;
-                            break;
-                        }
-                        ptx::tc_fence_after_sync();
-                    }
-                    if (warp == 0) TRACE(2, (int)si, 3 + 2 * h);
-                    ptx::tmem_st32(lane_addr + C::kACol0 + as * 64 + h * 32, A);
-                }
-                if (!ok) break;
-                ptx::tc_wait_st();
-                ptx::tc_fence_before_sync();
-                __syncwarp();
-                if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&bars.ab_full[as]));
-                if (warp == 0) TRACE(2, (int)si, 6);
-            }
-            if (!ok) break;
-
-            // ---- epilogue of this segment: accumulator -> registers -> fp16 rows of `out` (or a partial tile) ----
+            const int col = (warp & 3) * 32 + lane;
+            const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
+            if (warp == kEpiWarp0 || (!C::kEpiWarps && warp == 0)) TRACE(3, (int)seg, 0);
             if (!ptx::mbar_wait(ptx::smem_u32(&bars.d_full), seg & 1u)) {
                 if (lane == 0) atomicExch(p.status, 33);
-                ok = false;
-                break;
+                return false;
             }
             ptx::tc_fence_after_sync();
+            if (warp == kEpiWarp0 || (!C::kEpiWarps && warp == 0)) TRACE(3, (int)seg, 1);
             const bool complete = (u0 == 0) && (u1 == (int)U);
             const int scol = ct * 128 + col;
             const bool col_ok = scol < p.S;
@@ -488,25 +423,51 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
             const int nrows = min(NT, p.rows - row0);
             float* slot = nullptr;
             if (C::kSplit && !complete) slot = p.partials + ((size_t)b * 2 + (first_segment ? 0 : 1)) * (32 * 128);
-            constexpr int kChunks = NT / 16;                 // 16 accumulator columns at a time, dealt round-robin to the warpgroups
-            constexpr int kMyLast = ((kChunks - 1) / C::kWG) * C::kWG;   // index of the last round
-            if (wg >= kChunks) {                             // nothing to read for this warpgroup
-                __syncwarp();
-                if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&bars.d_empty));
-            }
+            if (C::kEpiWarps) {
+                // 16 accumulator columns (= 16 output rows) at a time: transposed through a 4 KB shared-memory tile so that
+                // the global stores are 16-byte rows instead of one 2-byte element per lane
+                const uint32_t stage_tile = epi_tile;                       // [16 rows][128 columns] fp16
+                const int t128 = (warp & 3) * 32 + lane;
 #pragma unroll 1
-            for (int ch = wg; ch < kChunks; ch += C::kWG) {
-                const int j0 = ch * 16;
-                uint32_t v[16];
-                ptx::tmem_ld16(lane_addr + j0, v);
+                for (int j0 = 0; j0 < NT; j0 += 16) {
+                    uint32_t v[16];
+                    ptx::tmem_ld16(lane_addr + j0, v);
+                    ptx::tc_wait_ld();
+                    if (j0 + 16 >= NT) {                   // the last columns are in registers: the accumulator is free again
+                        ptx::tc_fence_before_sync();
+                        __syncwarp();
+                        if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&bars.d_empty));
+                    }
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        ptx::sts16(stage_tile + j * 256 + col * 2, __half_as_ushort(__float2half_rn(__uint_as_float(v[j]))));
+                    ptx::named_bar_sync(1, 128);
+#pragma unroll
+                    for (int r = 0; r < 2; ++r) {
+                        const int idx = t128 + r * 128;                     // 256 chunks of 16 bytes: row = idx / 16, chunk = idx % 16
+                        const int m = j0 + (idx >> 4), c8 = (idx & 15) * 8;
+                        if (m < nrows && ct * 128 + c8 < p.S) {
+                            const uint4 q = ptx::lds128(stage_tile + (idx >> 4) * 256 + c8 * 2);
+                            *reinterpret_cast<uint4*>(p.out + (size_t)(row0 + m) * p.S + ct * 128 + c8) = q;
+                        }
+                    }
+                    ptx::named_bar_sync(1, 128);
+                }
+            } else {
+            constexpr int CH = NT >= 32 ? 32 : 16;          // accumulator columns per tensor-memory load
+#pragma unroll 1
+            for (int j0 = 0; j0 < NT; j0 += CH) {
+                uint32_t v[CH];
+                if (CH == 32) ptx::tmem_ld32(lane_addr + j0, reinterpret_cast<uint32_t(&)[32]>(v));
+                else ptx::tmem_ld16(lane_addr + j0, reinterpret_cast<uint32_t(&)[16]>(v));
                 ptx::tc_wait_ld();
-                if (ch + C::kWG >= kChunks) {              // this warp's last chunk is in registers: its part of the accumulator is free
+                if (j0 + CH >= NT) {                       // the last columns are in registers: the accumulator is free again
                     ptx::tc_fence_before_sync();
                     __syncwarp();
                     if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&bars.d_empty));
                 }
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
+                for (int j = 0; j < CH; ++j) {
                     const int m = j0 + j;
                     if (m < nrows) {
                         float f = __uint_as_float(v[j]);
@@ -520,23 +481,24 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
                     }
                 }
             }
-            (void)kMyLast;
+            }
+            if (warp == kEpiWarp0 || (!C::kEpiWarps && warp == 0)) TRACE(3, (int)seg, 2);
             if (C::kSplit && !complete) {
                 const long long T = n_tiles * U;
                 __threadfence();
-                ptx::named_bar_sync(1, 128 * C::kWG);
+                ptx::named_bar_sync(1, 128);
                 const long long lo_t = tile * U, hi_t = lo_t + U - 1;
                 const int b_lo = range_owner(T, G, lo_t), b_hi = range_owner(T, G, hi_t);
-                if (threadIdx.x == 0) {
+                if ((warp & 3) == 0 && lane == 0) {
                     const unsigned int prev = atomicAdd(p.counters + tile, 1u);
                     s_last = (prev == (unsigned int)(b_hi - b_lo)) ? 1 : 0;
                 }
-                ptx::named_bar_sync(1, 128 * C::kWG);
+                ptx::named_bar_sync(1, 128);
                 if (s_last) {
                     // the last CTA to arrive sums the partial tiles in CTA order: a fixed order, so results are reproducible
                     __threadfence();
                     const bool lo_starts_here = range_lo(T, G, b_lo) == lo_t;
-                    if (col_ok && wg == 0) {
+                    if (col_ok) {
                         for (int m = 0; m < nrows; ++m) {
                             float f = 0.f;
                             for (int bb = b_lo; bb <= b_hi; ++bb) {
@@ -548,13 +510,108 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
                             *o = __float2half_rn(f);
                         }
                     }
-                    if (threadIdx.x == 0) p.counters[tile] = 0;     // leave the scratch ready for the next launch
+                    if ((warp & 3) == 0 && lane == 0) p.counters[tile] = 0;     // leave the scratch ready for the next launch
                 }
-                ptx::named_bar_sync(1, 128 * C::kWG);
+                ptx::named_bar_sync(1, 128);
             }
-            ++seg;
-            t += u1 - u0;
-            first_segment = false;
+            return true;
+        };
+
+        if (C::kEpiWarps && warp >= kEpiWarp0) {
+            // ----- dedicated epilogue warps: one pass per segment -----
+            uint32_t seg = 0;
+            bool first_segment = true;
+            for (long long t = t_lo; t < t_hi;) {
+                const long long tile = t / U;
+                const int u0 = (int)(t - tile * U);
+                const int u1 = (int)min(U, u0 + (t_hi - t));
+                if (!epilogue(seg, tile, u0, u1, first_segment)) break;
+                ++seg;
+                t += u1 - u0;
+                first_segment = false;
+            }
+        } else {
+            // ----- dequant warps -----
+            const int wg = warp >> 2;                                           // warpgroup: takes every kWG-th weight stage
+            const int col = (warp & 3) * 32 + lane;                             // weight column in the tile = tensor-memory lane
+            const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
+            uint32_t si = 0, seg = 0;
+            bool ok = true;
+            bool first_segment = true;
+            for (long long t = t_lo; t < t_hi && ok;) {
+                const long long tile = t / U;
+                const int u0 = (int)(t - tile * U);
+                const int u1 = (int)min(U, u0 + (t_hi - t));
+                for (int u = u0; u < u1 && ok; ++u, ++si) {
+                    if ((int)(si % C::kWG) != wg) continue;
+                    const uint32_t ws = si % kWStages, wph = (si / kWStages) & 1u;
+                    if (warp == 0) TRACE(2, (int)si, 0);
+                    if (!ptx::mbar_wait(ptx::smem_u32(&bars.w_full[ws]), wph)) {
+                        if (lane == 0) atomicExch(p.status, 31);
+                        ok = false;
+                        break;
+                    }
+                    if (warp == 0) TRACE(2, (int)si, 1);
+                    const uint32_t st = w_ring + ws * WS::kBytes;
+                    const uint32_t g0 = p.gdiv(2u * (uint32_t)u);
+                    const uint32_t as = si % kABStages, aph = (si / kABStages) & 1u;
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        ColK c;
+                        {
+                            const uint32_t row = (h == 0) ? 0u : (p.gdiv(2u * (uint32_t)u + 1u) - g0);   // 0 or 1
+                            const uint32_t sz = ptx::lds32(st + WS::kS + row * 256 + (col & ~1) * 2) >> (16 * (col & 1));
+                            const uint32_t zz = ptx::lds32(st + WS::kZ + row * 256 + (col & ~1) * 2) >> (16 * (col & 1));
+                            c.s2 = prmt(sz, sz, 0x1010);
+                            c.z2 = prmt(zz, zz, 0x1010);
+                        }
+                        // fast mode needs: scale sign clear, zero-point an integer in [0, 512] ([0, 255] for the sparse format)
+                        const uint32_t zr = hadd2_u(hadd2_u(c.z2, kMagic1024), H2_N1024);
+                        constexpr uint32_t kAdd = SPARSE ? 0x2407u : 0x1FFFu;
+                        const uint32_t zlo = c.z2 & 0xFFFFu;
+                        const uint32_t not_fast = ((zlo | ((zlo & 0x7FFFu) + kAdd) | c.s2) & 0x8000u) | (zr ^ c.z2);
+                        const uint32_t wb = st + WS::kW + h * (F::WROWS * 512) + col * 4;
+                        const uint32_t mb = st + WS::kMask + h * (F::MROWS * 512) + col * 4;
+                        uint32_t A[32];
+                        if (!__any_sync(0xFFFFFFFFu, not_fast != 0)) {
+                            if (SPARSE) c.zb = __half2uint_rz(__ushort_as_half((unsigned short)zlo)) * 0x01010101u;
+                            F::template decode<MODE_FAST>(wb, mb, c, A, lut);
+                        } else {
+                            c.zb = 0;
+                            const bool lin = __hge(__ushort_as_half((unsigned short)(c.s2 & 0xFFFFu)), __ushort_as_half(0));
+                            if (__all_sync(0xFFFFFFFFu, lin)) F::template decode<MODE_GENERAL>(wb, mb, c, A, lut);
+                            else F::template decode<MODE_SLOW>(wb, mb, c, A, lut);
+                        }
+                        if (h == 1) {
+                            __syncwarp();
+                            if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&bars.w_empty[ws]));   // both halves are in registers now
+                        }
+                        if (warp == 0) TRACE(2, (int)si, 2 + 2 * h);
+                        if (h == 0) {
+                            // the A stage (and its activation tile) is free once the MMAs of its previous use have completed
+                            if (!ptx::mbar_wait(ptx::smem_u32(&bars.ab_free[as]), aph ^ 1u)) {
+                                if (lane == 0) atomicExch(p.status, 32);
+                                ok = false;
+                                break;
+                            }
+                            ptx::tc_fence_after_sync();
+                        }
+                        if (warp == 0) TRACE(2, (int)si, 3 + 2 * h);
+                        ptx::tmem_st32(lane_addr + C::kACol0 + as * 64 + h * 32, A);
+                    }
+                    if (!ok) break;
+                    ptx::tc_wait_st();
+                    ptx::tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&bars.ab_full[as]));
+                    if (warp == 0) TRACE(2, (int)si, 6);
+                }
+                if (!ok) break;
+                if (!C::kEpiWarps && wg == 0) ok = epilogue(seg, tile, u0, u1, first_segment);
+                ++seg;
+                t += u1 - u0;
+                first_segment = false;
+            }
         }
     }
 
@@ -620,7 +677,8 @@ int launch_nt(const UmmaParams& p, const __half* x, int n_groups, cudaStream_t s
     ok = ok && encode_2d(&tm.z, p.zeros, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, n_groups, p.S, 2, 128, CU_TENSOR_MAP_SWIZZLE_NONE);
     if (!ok) return I4MM_ERR_DEVICE;
 
-    const size_t smem = 1024 + (size_t)kABStages * C::kBStageBytes + (size_t)kWStages * WStage<F>::kBytes;
+    const size_t smem = 1024 + (size_t)kABStages * C::kBStageBytes + (size_t)kWStages * WStage<F>::kBytes +
+                        (C::kEpiWarps ? 4096 : 0);
     auto kern = umma_kernel<BITS, SPARSE, NT>;
     static int ctas_per_sm[16] = {0};
     static int sm_count[16] = {0};
@@ -655,16 +713,47 @@ int launch_nt(const UmmaParams& p, const __half* x, int n_groups, cudaStream_t s
     return I4MM_OK;
 }
 
+// Rows per tile (the MMA's N).  Few rows: the smallest tile that holds them.  Many rows: the tile height that
+// minimises (waves of tiles over the SMs) x (time per tile), so that e.g. 320 tiles of 256 rows (2.2 waves on 148
+// SMs) become 440 tiles of 192 rows (3.0 waves) when that is faster.
+int choose_tile_rows(int rows, int col_tiles, int sms) {
+    if (rows <= 16) return 16;
+    if (rows <= 32) return 32;
+    if (rows <= 64) return 64;
+    if (rows <= 128) return 128;
+    const int cand[4] = {256, 224, 192, 160};
+    int best = 256;
+    long long best_cost = -1;
+    for (int i = 0; i < 4; ++i) {
+        const int nt = cand[i];
+        const long long tiles = (long long)((rows + nt - 1) / nt) * col_tiles;
+        const long long waves = (tiles + sms - 1) / sms;
+        const long long cost = waves * (nt + 24);          // + per-tile fill / drain, in row units
+        if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = nt; }
+    }
+    return best;
+}
+
 template <int BITS, bool SPARSE>
 int launch_fmt(UmmaParams& p, const __half* x, int n_groups, cudaStream_t stream, cudaError_t* cuda_err) {
-    const int rows = p.rows;
-    const int nt = rows <= 16 ? 16 : rows <= 32 ? 32 : rows <= 64 ? 64 : rows <= 128 ? 128 : 256;
-    p.MTILES = (rows + nt - 1) / nt;
+    static int sms = 0;
+    if (sms == 0) {
+        int dev = 0, n = 0;
+        if (cudaGetDevice(&dev) == cudaSuccess && cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0)
+            sms = n;
+        else
+            sms = 148;
+    }
+    const int nt = choose_tile_rows(p.rows, p.CT, sms);
+    p.MTILES = (p.rows + nt - 1) / nt;
     switch (nt) {
         case 16: return launch_nt<BITS, SPARSE, 16>(p, x, n_groups, stream, cuda_err);
         case 32: return launch_nt<BITS, SPARSE, 32>(p, x, n_groups, stream, cuda_err);
         case 64: return launch_nt<BITS, SPARSE, 64>(p, x, n_groups, stream, cuda_err);
         case 128: return launch_nt<BITS, SPARSE, 128>(p, x, n_groups, stream, cuda_err);
+        case 160: return launch_nt<BITS, SPARSE, 160>(p, x, n_groups, stream, cuda_err);
+        case 192: return launch_nt<BITS, SPARSE, 192>(p, x, n_groups, stream, cuda_err);
+        case 224: return launch_nt<BITS, SPARSE, 224>(p, x, n_groups, stream, cuda_err);
         default: return launch_nt<BITS, SPARSE, 256>(p, x, n_groups, stream, cuda_err);
     }
 }
