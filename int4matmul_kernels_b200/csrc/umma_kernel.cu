@@ -222,11 +222,14 @@ struct WStage {     // one stage of the packed-weight ring: 128 k = two 64-k hal
     static constexpr int kBytes = kZ + 512;
 };
 
-constexpr int kWStages = 3;          // packed-weight ring (128 k per stage)
+constexpr int kMaxWStages = 8;
 constexpr int kABStages = 3;         // ring of (A in tensor memory, activation tile in shared memory) pairs, 128 k per stage
 
 template <int NT>
 struct Cfg {
+    // packed-weight ring (128 k per stage).  Few rows: the kernel streams weights from HBM, and the ring has to
+    // cover the DRAM latency; many rows: weights are a trickle next to the activation tiles
+    static constexpr int kWStages = NT <= 64 ? 8 : 3;
     static constexpr int kWG = 2;                                     // dequant warpgroups (4 warps each), alternating units
     static constexpr bool kEpiWarps = NT >= 128;                      // a warpgroup of its own for the epilogue (else dequant warpgroup 0 does it)
     static constexpr int kWarps = 4 * kWG + (kEpiWarps ? 4 : 0) + 3;  // + weight producer, activation producer, MMA issuer
@@ -242,7 +245,7 @@ struct Cfg {
 };
 
 struct Barriers {
-    unsigned long long w_full[kWStages], w_empty[kWStages];
+    unsigned long long w_full[kMaxWStages], w_empty[kMaxWStages];
     unsigned long long ab_full[kABStages];     // 4 dequant warps + the activation producer (with its transaction bytes)
     unsigned long long ab_free[kABStages];     // tcgen05.commit: the MMAs that read the stage are done
     unsigned long long d_full, d_empty;
@@ -279,10 +282,10 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
     const uint32_t smem0 = (ptx::smem_u32(smem) + 1023u) & ~1023u;
     const uint32_t b_ring = smem0;
     const uint32_t w_ring = smem0 + kABStages * C::kBStageBytes;
-    const uint32_t epi_tile = w_ring + kWStages * WS::kBytes;     // 4 KB transposition tile of the epilogue warps (NT >= 128)
+    const uint32_t epi_tile = w_ring + C::kWStages * WS::kBytes;     // 4 KB transposition tile of the epilogue warps (NT >= 128)
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < kWStages; ++i) {
+        for (int i = 0; i < C::kWStages; ++i) {
             ptx::mbar_init(ptx::smem_u32(&bars.w_full[i]), 1);
             ptx::mbar_init(ptx::smem_u32(&bars.w_empty[i]), 4);
         }
@@ -328,44 +331,54 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
         // =========================== packed weights + scales / zeros: one thread ===========================
         if (lane == 0) {
             constexpr uint32_t kBytes = (uint32_t)WS::kBytes;      // every box is copied whole (out-of-range parts are zero-filled)
-            uint32_t si = 0;
-            for (long long t = t_lo; t < t_hi; ++t, ++si) {
-                const long long tile = t / U;
-                const int u = (int)(t - tile * U);
+            uint32_t si = 0, ws = 0, wph = 0;
+            bool ok = true;
+            for (long long t = t_lo; t < t_hi && ok;) {
+                const long long tile = t / U;                      // one 64-bit division per segment, none per unit
+                const int u0 = (int)(t - tile * U);
+                const int u1 = (int)min(U, u0 + (t_hi - t));
                 const int ct = (int)(tile % p.CT);
-                const uint32_t ws = si % kWStages, wph = (si / kWStages) & 1u;
-                TRACE(0, (int)si, 0);
-                if (!ptx::mbar_wait(ptx::smem_u32(&bars.w_empty[ws]), wph ^ 1u)) { atomicExch(p.status, 11); break; }
-                TRACE(0, (int)si, 1);
-                const uint32_t st = w_ring + ws * WS::kBytes, full = ptx::smem_u32(&bars.w_full[ws]);
-                ptx::mbar_arrive_expect_tx(full, kBytes);
-                ptx::tma_load_2d(st + WS::kW, &tm.w, ct * 128, u * 2 * F::WROWS, full);
-                if (SPARSE) ptx::tma_load_2d(st + WS::kMask, &tm.m, ct * 128, u * 2 * F::MROWS, full);
-                const int g0 = (int)p.gdiv(2u * (uint32_t)u);
-                ptx::tma_load_2d(st + WS::kS, &tm.s, ct * 128, g0, full);
-                ptx::tma_load_2d(st + WS::kZ, &tm.z, ct * 128, g0, full);
-                TRACE(0, (int)si, 2);
+                for (int u = u0; u < u1; ++u, ++si) {
+                    TRACE(0, (int)si, 0);
+                    if (!ptx::mbar_wait(ptx::smem_u32(&bars.w_empty[ws]), wph ^ 1u)) { atomicExch(p.status, 11); ok = false; break; }
+                    TRACE(0, (int)si, 1);
+                    const uint32_t st = w_ring + ws * WS::kBytes, full = ptx::smem_u32(&bars.w_full[ws]);
+                    ptx::mbar_arrive_expect_tx(full, kBytes);
+                    ptx::tma_load_2d(st + WS::kW, &tm.w, ct * 128, u * 2 * F::WROWS, full);
+                    if (SPARSE) ptx::tma_load_2d(st + WS::kMask, &tm.m, ct * 128, u * 2 * F::MROWS, full);
+                    const int g0 = (int)p.gdiv(2u * (uint32_t)u);
+                    ptx::tma_load_2d(st + WS::kS, &tm.s, ct * 128, g0, full);
+                    ptx::tma_load_2d(st + WS::kZ, &tm.z, ct * 128, g0, full);
+                    TRACE(0, (int)si, 2);
+                    if (++ws == C::kWStages) { ws = 0; wph ^= 1u; }
+                }
+                t += u1 - u0;
             }
         }
     } else if (warp == kBProducer) {
         // =========================== activation tiles, two 64-k sub-tiles per unit: one thread ===========================
         if (lane == 0) {
-            uint32_t si = 0;
-            for (long long t = t_lo; t < t_hi; ++t, ++si) {
+            uint32_t s = 0, ph = 0;
+            bool ok = true;
+            for (long long t = t_lo; t < t_hi && ok;) {
                 const long long tile = t / U;
-                const int u = (int)(t - tile * U);
+                const int u0 = (int)(t - tile * U);
+                const int u1 = (int)min(U, u0 + (t_hi - t));
                 const int mt = (int)(tile / p.CT);
-                const uint32_t s = si % kABStages, ph = (si / kABStages) & 1u;
-                if (!ptx::mbar_wait(ptx::smem_u32(&bars.ab_free[s]), ph ^ 1u)) { atomicExch(p.status, 12); break; }
-                const uint32_t full = ptx::smem_u32(&bars.ab_full[s]);
-                ptx::mbar_arrive_expect_tx(full, (uint32_t)C::kBStageBytes);
-                ptx::tma_load_2d(b_ring + s * C::kBStageBytes, &tm.x, u * 128, mt * NT, full);
-                ptx::tma_load_2d(b_ring + s * C::kBStageBytes + C::kBHalfBytes, &tm.x, u * 128 + 64, mt * NT, full);
+                for (int u = u0; u < u1; ++u) {
+                    if (!ptx::mbar_wait(ptx::smem_u32(&bars.ab_free[s]), ph ^ 1u)) { atomicExch(p.status, 12); ok = false; break; }
+                    const uint32_t full = ptx::smem_u32(&bars.ab_full[s]);
+                    ptx::mbar_arrive_expect_tx(full, (uint32_t)C::kBStageBytes);
+                    ptx::tma_load_2d(b_ring + s * C::kBStageBytes, &tm.x, u * 128, mt * NT, full);
+                    ptx::tma_load_2d(b_ring + s * C::kBStageBytes + C::kBHalfBytes, &tm.x, u * 128 + 64, mt * NT, full);
+                    if (++s == kABStages) { s = 0; ph ^= 1u; }
+                }
+                t += u1 - u0;
             }
         }
     } else if (warp == kMma) {
-        // =========================== MMA issuer: one thread ===========================
-        if (lane == 0) {
+        // =========================== MMA issuer: the warp walks the loop, one elected lane issues ===========================
+        {
             const uint32_t idesc = ptx::idesc_f16_m128(NT);
             uint32_t si = 0, seg = 0;
             bool ok = true;
@@ -374,28 +387,41 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
                 const int u0 = (int)(t - tile * U);
                 const int u1 = (int)min(U, u0 + (t_hi - t));
                 TRACE(3, (int)seg, 4);
-                if (!ptx::mbar_wait(ptx::smem_u32(&bars.d_empty), (seg & 1u) ^ 1u)) { atomicExch(p.status, 21); ok = false; break; }
+                if (!ptx::mbar_wait(ptx::smem_u32(&bars.d_empty), (seg & 1u) ^ 1u)) {
+                    if (lane == 0) atomicExch(p.status, 21);
+                    ok = false;
+                    break;
+                }
                 TRACE(3, (int)seg, 5);
                 ptx::tc_fence_after_sync();
+                uint32_t s = si % kABStages, ph = (si / kABStages) & 1u;
                 for (int u = u0; u < u1; ++u, ++si) {
-                    const uint32_t s = si % kABStages, ph = (si / kABStages) & 1u;
                     TRACE(1, (int)si, 0);
-                    if (!ptx::mbar_wait(ptx::smem_u32(&bars.ab_full[s]), ph)) { atomicExch(p.status, 22); ok = false; break; }
+                    if (!ptx::mbar_wait(ptx::smem_u32(&bars.ab_full[s]), ph)) {
+                        if (lane == 0) atomicExch(p.status, 22);
+                        ok = false;
+                        break;
+                    }
                     TRACE(1, (int)si, 1);
                     ptx::tc_fence_after_sync();
                     const uint64_t bdesc = ptx::smem_desc_sw128(b_ring + s * C::kBStageBytes);
                     const uint32_t a0 = tmem_base + C::kACol0 + s * 64;
+                    if (ptx::elect_one()) {
 #pragma unroll
-                    for (int k = 0; k < 8; ++k) {
-                        // K = 16 per instruction: +8 columns of A; B: +32 bytes (2 descriptor units) inside a 64-k sub-tile
-                        const uint64_t bd = bdesc + (uint64_t)((k >> 2) * (C::kBHalfBytes >> 4) + (k & 3) * 2);
-                        ptx::umma_f16_ts(tmem_base, a0 + k * 8, bd, idesc, (u > u0 || k > 0) ? 1u : 0u);
+                        for (int k = 0; k < 8; ++k) {
+                            // K = 16 per instruction: +8 columns of A; B: +32 bytes (2 descriptor units) inside a 64-k sub-tile
+                            const uint64_t bd = bdesc + (uint64_t)((k >> 2) * (C::kBHalfBytes >> 4) + (k & 3) * 2);
+                            ptx::umma_f16_ts(tmem_base, a0 + k * 8, bd, idesc, (u > u0 || k > 0) ? 1u : 0u);
+                        }
+                        ptx::tc_commit(ptx::smem_u32(&bars.ab_free[s]));
                     }
-                    ptx::tc_commit(ptx::smem_u32(&bars.ab_free[s]));
+                    __syncwarp();
                     TRACE(1, (int)si, 2);
+                    if (++s == kABStages) { s = 0; ph ^= 1u; }
                 }
                 if (!ok) break;
-                ptx::tc_commit(ptx::smem_u32(&bars.d_full));
+                if (ptx::elect_one()) ptx::tc_commit(ptx::smem_u32(&bars.d_full));
+                __syncwarp();
                 TRACE(3, (int)seg, 6);
                 ++seg;
                 t += u1 - u0;
@@ -543,8 +569,8 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
                 const int u0 = (int)(t - tile * U);
                 const int u1 = (int)min(U, u0 + (t_hi - t));
                 for (int u = u0; u < u1 && ok; ++u, ++si) {
+                    const uint32_t ws = si % C::kWStages, wph = (si / C::kWStages) & 1u;     // constants: multiply-shift, no division
                     if ((int)(si % C::kWG) != wg) continue;
-                    const uint32_t ws = si % kWStages, wph = (si / kWStages) & 1u;
                     if (warp == 0) TRACE(2, (int)si, 0);
                     if (!ptx::mbar_wait(ptx::smem_u32(&bars.w_full[ws]), wph)) {
                         if (lane == 0) atomicExch(p.status, 31);
@@ -677,7 +703,7 @@ int launch_nt(const UmmaParams& p, const __half* x, int n_groups, cudaStream_t s
     ok = ok && encode_2d(&tm.z, p.zeros, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, n_groups, p.S, 2, 128, CU_TENSOR_MAP_SWIZZLE_NONE);
     if (!ok) return I4MM_ERR_DEVICE;
 
-    const size_t smem = 1024 + (size_t)kABStages * C::kBStageBytes + (size_t)kWStages * WStage<F>::kBytes +
+    const size_t smem = 1024 + (size_t)kABStages * C::kBStageBytes + (size_t)C::kWStages * WStage<F>::kBytes +
                         (C::kEpiWarps ? 4096 : 0);
     auto kern = umma_kernel<BITS, SPARSE, NT>;
     static int ctas_per_sm[16] = {0};
