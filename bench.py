@@ -49,6 +49,9 @@ WORKLOADS = {
     "int3_matmul_m2048_20480x5120": dict(bits=3, n=20480, s=5120, m=2048, g=64, sparse=False),
     "int2_matmul_m2048_20480x5120": dict(bits=2, n=20480, s=5120, m=2048, g=64, sparse=False),
 }
+# 13B-class decoder linear-layer stack (hidden 5120, MLP 13824, 40 layers, int4, group 128), column-sharded over
+# the ranks with an all-gather of every matrix's outputs; "m" = activation rows
+STACK_WORKLOADS = {f"stack13b_m{m}": m for m in (1, 16, 128, 2048)}
 DEFAULT_WORKLOAD = "int4_matmul_m2048_5120x20480"
 
 # DRAM bytes per launch of the dominant kernel from ncu captures (dram__bytes_read.sum + dram__bytes_write.sum);
@@ -184,12 +187,169 @@ def run_reference(args, w, name):
     print(json.dumps(line))
 
 
+def run_stack(args):
+    """The layer-stack workloads: every rank holds its column shard of every matrix; each matrix's outputs are
+    all-gathered (NCCL) before the next one reads them.  One step = one pass of the activations through all layers."""
+    import torch
+    import torch.distributed as dist
+    from int4matmul_kernels_b200 import capi, sharding
+
+    m = STACK_WORKLOADS[args.workload]
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    cfg = sharding.StackConfig(layers=args.layers)
+    kind = "hbm" if m <= 64 else "tensor"
+    unit = "GB/s" if kind == "hbm" else "TFLOP/s"
+    wpl = cfg.weights_per_layer()
+    groups_per_layer = sum((n // cfg.group_size) * s for _, n, s in cfg.matrices())
+    act_per_layer = sum(m * (n + s) * 2 for _, n, s in cfg.matrices())
+    bytes_pass = cfg.layers * (wpl // 2 + groups_per_layer * 4 + act_per_layer)          # int4 weights + scales + zeros + x + out
+    flops_pass = cfg.layers * 2.0 * m * wpl
+    metric = f"13B-class int4 linear stack, M={m}: " + ("effective HBM GB/s" if kind == "hbm" else "TFLOP/s")
+    units = bytes_pass / 1e9 if kind == "hbm" else flops_pass / 1e12
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        cores = os.cpu_count() or 1
+        torch.set_num_threads(cores)
+        # bounded sample: one layer's four (concatenated) matrices at reduced row count, scaled to 40 layers
+        sec = 0.0
+        rows = min(m, 64)
+        for name, n, s_full in cfg.matrices():
+            wl = dict(bits=4, n=n, s=s_full, m=rows, g=cfg.group_size, sparse=False)
+            p = cpu_problem(wl)
+            t_deq, t_mm = __import__("oracle.cpu_baseline", fromlist=["timed_pass"]).timed_pass(p, rows, cores)
+            sec += t_deq + t_mm * (m / rows)
+        sec *= cfg.layers
+        value = units / sec
+        sample = f"one layer (4 launches' matrices), dequantise timed whole, matmul on {rows} of {m} rows scaled; x{cfg.layers} layers"
+        print(json.dumps(dict(metric=metric, value=value, unit=unit, n_gpus=args.gpus, steps=args.steps, warmup=args.warmup,
+                              ms_per_step=sec * 1e3, higher_is_better=True, scaling="strong", vs_baseline=None, dtype="f16",
+                              data="synthetic", impl="reference", config=dict(workload=args.workload, layers=cfg.layers, m=m),
+                              cpu_baseline=dict(value=value, unit=unit, cores=cores, kind="port", sample=sample),
+                              e2e=dict(value=value, unit=unit, h2d_bytes_per_step=0, d2h_bytes_per_step=0))))
+        return
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the operator has no CPU path")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    capi.load()
+    stack = sharding.DecoderStack(cfg, rank, world, dev)
+    gen = torch.Generator().manual_seed(4321)
+    h_host = torch.randn((m, cfg.hidden), generator=gen).to(torch.float16).pin_memory()
+    h0 = h_host.to(dev)
+
+    def step():
+        return stack.forward(h0)
+
+    for _ in range(max(args.warmup, 3)):
+        out = step()
+    torch.cuda.synchronize()
+    graph = None
+    if not args.no_graph:
+        try:
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                step()
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                for _ in range(args.steps):
+                    out = step()
+            graph.replay()
+            torch.cuda.synchronize()
+        except Exception as e:
+            print(f"[bench] CUDA graph capture unavailable ({type(e).__name__}: {e}); timing direct launches", file=sys.stderr)
+            graph = None
+
+    def run_steps():
+        if graph is not None:
+            graph.replay()
+        else:
+            for _ in range(args.steps):
+                step()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    with ClockSampler(local_rank) as clocks:
+        run_steps()
+        barrier()
+        e0.record()
+        run_steps()
+        e1.record()
+        barrier()
+        run_steps()
+        barrier()
+    ms_total = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms_total], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total = float(t.item())
+    ms_step = ms_total / args.steps
+    value = units / (ms_step / 1e3)
+
+    # end to end: activations from pinned host memory in, final activations back, every step
+    out_host = torch.empty((m, cfg.hidden), dtype=torch.float16).pin_memory()
+    h_dev = torch.empty_like(h0)
+
+    def e2e_step():
+        h_dev.copy_(h_host, non_blocking=True)
+        out_host.copy_(stack.forward(h_dev), non_blocking=True)
+
+    e2e_step()
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    ms_e2e = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms_e2e], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_e2e = float(t.item())
+
+    peaks = measured_peaks()
+    peak = peaks["hbm"] if kind == "hbm" else peaks["tf_sustained"]
+    achieved = value / world                                    # per GPU: every rank moves / computes 1/world of the pass
+    if rank == 0:
+        print(json.dumps(dict(
+            metric=metric, value=value, unit=unit, n_gpus=world, steps=args.steps, warmup=max(args.warmup, 3),
+            ms_per_step=ms_step, higher_is_better=True, scaling="strong", vs_baseline=None, dtype="f16", data="synthetic",
+            config=dict(workload=args.workload, layers=cfg.layers, hidden=cfg.hidden, mlp=cfg.mlp, m=m, bits=4, g=cfg.group_size,
+                        sharding=f"S columns of every matrix over {world} GPU(s), all-gather after each of the 4 launches per layer",
+                        l2=f"{cfg.layers * wpl // 2 / 1e9:.1f} GB of weights per pass (>> L2)",
+                        timed_as="one CUDA graph of the K steps" if graph is not None else "K direct launches"),
+            roofline=dict(bound=kind, achieved=achieved, peak=peak, unit=unit, frac=achieved / peak, traffic=None,
+                          peak_source=peaks["source"], kernel="umma_kernel (tcgen05)",
+                          note="whole pass incl. normalisation kernels and all-gathers, per GPU; sustained peak for tensor"),
+            cpu_baseline=None,
+            e2e=dict(value=units / (ms_e2e / args.steps / 1e3), unit=unit, h2d_bytes_per_step=h_host.numel() * 2,
+                     d2h_bytes_per_step=out_host.numel() * 2, ms_per_step=ms_e2e / args.steps),
+            clocks=clocks.summary(), gpu_launches=args.steps * cfg.layers * 4)))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS) + sorted(STACK_WORKLOADS))
+    ap.add_argument("--layers", type=int, default=40, help="layers of the stack workloads")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--path", type=int, default=0, help="0 auto, 1 streaming kernel, 2 tcgen05 kernel")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -197,6 +357,9 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="launch the timed steps directly instead of as one CUDA graph")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 0)
+    if args.workload in STACK_WORKLOADS:
+        run_stack(args)
+        return
     w = WORKLOADS[args.workload]
     if args.impl == "reference":
         run_reference(args, w, args.workload)
