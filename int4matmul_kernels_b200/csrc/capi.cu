@@ -9,6 +9,8 @@ cudaError_t stream_launch(int bits, bool sparse, StreamParams p, int total_rows,
 cudaError_t sparse_pack_launch(void* wt_out, void* msk_out, const void* wt_in, const void* msk_in,
                                int S, int N, void* violations, cudaStream_t stream);
 cudaError_t check_mask_launch(const void* mask, size_t count, void* violations, cudaStream_t stream);
+cudaError_t rownorm_launch(int mode, void* y, const void* a, const void* b, const void* c, long long rows, int width,
+                           long long sa, long long sb, long long sc, cudaStream_t stream);
 int umma_launch(int bits, bool sparse, const StreamParams& p, int total_rows, int n_groups, int group_size,
                 cudaStream_t stream, cudaError_t* cuda_err);
 bool umma_supported(int bits, bool sparse, int total_rows, int N, int S);
@@ -134,6 +136,22 @@ int i4mm_device_status(void* workspace, void* stream) {
     e = cudaMemsetAsync((char*)workspace + kStatusOffset, 0, sizeof(int), (cudaStream_t)stream);
     if (e != cudaSuccess) return fail_cuda(e);
     return I4MM_ERR_TIMEOUT;
+}
+
+int i4mm_row_norm(int mode, void* y, const void* a, const void* b, const void* c, int64_t rows, int64_t width,
+                  int64_t stride_a, int64_t stride_b, int64_t stride_c, void* stream) {
+    if (mode < 0 || mode > 3 || rows < 0 || width <= 0 || width % 2 != 0 || width > (1 << 30) || rows > (1ll << 31) - 1)
+        return I4MM_ERR_SHAPE;
+    if (rows == 0) return I4MM_OK;
+    if (!y || !a || (mode != 0 && !b) || (mode == 1 && !c)) return I4MM_ERR_NULL;
+    if ((stride_a | stride_b | stride_c) & 1) return I4MM_ERR_ALIGN;
+    if ((reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) |
+         reinterpret_cast<uintptr_t>(c)) & 3u)
+        return I4MM_ERR_ALIGN;
+    const cudaError_t e = i4mm::rownorm_launch(mode, y, a, b, c, rows, (int)width, stride_a, stride_b, stride_c,
+                                               (cudaStream_t)stream);
+    if (e != cudaSuccess) return fail_cuda(e);
+    return I4MM_OK;
 }
 
 int i4mm_sparse_pack(void* wt_out, void* msk_out, const void* wt_in, const void* msk_in,

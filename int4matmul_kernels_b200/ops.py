@@ -160,3 +160,20 @@ def weight_matrix_packing(wt_outs, msk_outs, wt_in, msk_in) -> None:
         bad = int(violations.item())
     if bad:
         raise ValueError(f"weight_matrix_packing: {bad} block(s) of 32 weights do not keep exactly 16 (16:32 sparsity)")
+
+
+def row_norm(mode: int, a: torch.Tensor, b: torch.Tensor | None = None, c: torch.Tensor | None = None) -> torch.Tensor:
+    """Row-wise glue of the layer-stack runner (`i4mm_row_norm`): v / rms(v) per row with
+    v = a (mode 0), a + b + c (1), a + b / rms(b) (2), a * b (3).  Inputs fp16 (rows, width), last dim contiguous."""
+    rows, width = a.shape
+    for t in (a, b, c):
+        if t is not None and (t.dtype != torch.float16 or t.stride(-1) != 1 or tuple(t.shape) != (rows, width)):
+            raise ValueError("row_norm inputs must be fp16 (rows, width) with a contiguous last dim")
+    y = torch.empty((rows, width), dtype=torch.float16, device=a.device)
+    stream = torch.cuda.current_stream(a.device)
+    status = capi.load().i4mm_row_norm(
+        mode, y.data_ptr(), a.data_ptr(), b.data_ptr() if b is not None else None, c.data_ptr() if c is not None else None,
+        rows, width, a.stride(0), b.stride(0) if b is not None else 0, c.stride(0) if c is not None else 0, stream.cuda_stream)
+    if status != capi.OK:
+        raise Int4MatmulError(status, "row_norm")
+    return y

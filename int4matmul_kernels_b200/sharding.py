@@ -191,19 +191,28 @@ class DecoderStack:
         return [g[:, :, i, :].reshape(rows, -1) for i in range(parts)]
 
     @staticmethod
-    def norm(x: torch.Tensor) -> torch.Tensor:
-        f = x.float()
-        return (f * torch.rsqrt(f.pow(2).mean(dim=-1, keepdim=True) + 1e-6)).to(torch.float16)
+    def combine(mode: int, a: torch.Tensor, b: Optional[torch.Tensor] = None, c: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """v / rms(v) per row with v = a (mode 0), a + b + c (1), a + b / rms(b) (2), a * b (3), in fp32.
+        One fused kernel on CUDA tensors; the same expression in torch ops on CPU tensors (host-logic tests)."""
+        if a.is_cuda:
+            from . import ops
+            return ops.row_norm(mode, a, b, c)
+
+        def rn(f):
+            return f * torch.rsqrt(f.pow(2).mean(dim=-1, keepdim=True) + 1e-6)
+        fa = a.float()
+        v = fa if mode == 0 else fa + b.float() + c.float() if mode == 1 else fa + rn(b.float()) if mode == 2 else fa * b.float()
+        return rn(v).to(torch.float16)
 
     def forward(self, h: torch.Tensor) -> torch.Tensor:
-        norm = self.norm
+        comb = self.combine
         for mats in self.layers:
-            q, k, v = self._linear(mats["qkv"], norm(h), 3)
-            t = norm(q.float() + k.float() + v.float())
+            q, k, v = self._linear(mats["qkv"], comb(0, h), 3)
+            t = comb(1, q, k, v)
             (o,) = self._linear(mats["o"], t, 1)
-            h = norm(h.float() + norm(o).float())
+            h = comb(2, h, o)
             gate, up = self._linear(mats["gate_up"], h, 2)
-            a = norm(gate.float() * up.float())
+            a = comb(3, gate, up)
             (d,) = self._linear(mats["down"], a, 1)
-            h = norm(h.float() + norm(d).float())
+            h = comb(2, h, d)
         return h
