@@ -146,6 +146,46 @@ def cpu_reference_seconds(w, problem, rows, cores):
     return t_deq + t_mm * (w["m"] / rows)
 
 
+def reference_cuda_seconds(w, layer, x, torch):
+    """Times the UNMODIFIED reference's CUDA kernels (built into oracle/_ref by oracle/build_reference.py) on the same
+    tensors, beside the product: a baseline leg like the CPU one, never part of the product path.  None if absent."""
+    import glob
+    import importlib.util
+    cand = glob.glob(os.path.join(ROOT, "oracle", "_ref", "int4matmul_ref*.so"))
+    if not cand or (w["bits"] == 3 and w["m"] == 1):
+        return None
+    try:
+        spec = importlib.util.spec_from_file_location("int4matmul_ref", cand[0])
+        ref = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(ref)
+        out = torch.zeros((1, w["m"], layer["matrix"].shape[1]), dtype=torch.float16, device=x.device)
+
+        def call():
+            ref.quant_matmul(w["bits"], out, layer["matrix"], x, layer["scales"], layer["zeros"], w["g"], layer["mask"])
+
+        for _ in range(3):
+            call()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        iters = 10
+        e0.record()
+        for _ in range(iters):
+            call()
+        e1.record()
+        torch.cuda.synchronize()
+        sec = e0.elapsed_time(e1) / iters / 1e3
+        kind = metric_of(w)[2]
+        notes = ""
+        np_ = os.path.join(ROOT, "oracle", "_ref", "BUILD_NOTES.txt")
+        if os.path.exists(np_):
+            notes = open(np_).read().strip()
+        return dict(value=units_per_step(w, kind) / sec, unit=metric_of(w)[1], us_per_call=sec * 1e6,
+                    what="reference quant_matmul (its WMMA / CUDA-core kernels compiled for sm_100), same tensors, "
+                         "its own stream and temporaries, 10 calls", build_notes=notes)
+    except Exception as e:
+        return dict(unavailable=f"{type(e).__name__}: {e}")
+
+
 def metric_of(w):
     if w["m"] == 1:
         return "int4 matvec HBM GB/s".replace("int4", f"int{w['bits']}"), "GB/s", "hbm"
@@ -237,8 +277,10 @@ def run_stack(args):
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
+        import datetime
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=dev)
+        # a short collective timeout: a rank that never arrives ends the run with an error instead of a long hang
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=90))
     capi.load()
     stack = sharding.DecoderStack(cfg, rank, world, dev)
     gen = torch.Generator().manual_seed(4321)
@@ -252,7 +294,8 @@ def run_stack(args):
         out = step()
     torch.cuda.synchronize()
     graph = None
-    if not args.no_graph:
+    # with collectives inside the step, the steps are launched directly (no graph capture of NCCL calls)
+    if not args.no_graph and world == 1:
         try:
             side = torch.cuda.Stream()
             side.wait_stream(torch.cuda.current_stream())
@@ -529,6 +572,11 @@ def main():
                    sample=(f"full {w['n']}x{w['s']} dequantise timed whole, matmul timed on {rows} of {w['m']} rows and "
                            f"scaled to all rows, best of {reps}"))
 
+    # ---- the reference's own CUDA kernels on this GPU, when the build made by oracle/build_reference.py is present ----
+    ref_gpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        ref_gpu = reference_cuda_seconds(w, layers[0], x, torch)
+
     if rank == 0:
         line = dict(metric=metric, value=value, unit=unit, n_gpus=world, steps=args.steps, warmup=max(args.warmup, 3),
                     ms_per_step=ms_step, higher_is_better=True, scaling="strong", vs_baseline=None,
@@ -536,7 +584,7 @@ def main():
                     config=dict(workload=args.workload, **{k: w[k] for k in ("bits", "n", "s", "m", "g", "sparse")},
                                 sharding=f"S columns over {world} GPU(s)", l2="rotating %d weight copies (> 2x L2)" % copies,
                                 timed_as="one CUDA graph of the K steps" if graph is not None else "K direct launches"),
-                    roofline=roofline, cpu_baseline=cpu, e2e=e2e, clocks=clocks.summary(),
+                    roofline=roofline, cpu_baseline=cpu, reference_cuda=ref_gpu, e2e=e2e, clocks=clocks.summary(),
                     gpu_launches=args.steps * launches_per_step)
         print(json.dumps(line))
     if world > 1:

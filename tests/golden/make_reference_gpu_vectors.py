@@ -32,6 +32,10 @@ CASES = [
 ]
 # the reference's dense int3 matvec kernel is only run when its build notes say it assembled with optimisation
 INT3_MATVEC_CASE = (3, False, 256, 128, 1, 64, 111)
+# exponent coding (negative scales select it, matmul.cuh:127-136, 414-428): whole aligned 32-column runs of a group
+# switch together, as the reference's warp-uniform branch requires
+EXPONENT_CASES = [(4, False, 256, 128, 1, 64, 121), (4, False, 256, 128, 70, 64, 122), (2, False, 256, 128, 70, 64, 123),
+                  (4, True, 256, 128, 70, 64, 124)]
 
 
 def load_reference():
@@ -48,11 +52,11 @@ def main(out_path):
     ref = load_reference()
     dev = "cuda:0"
     blob = {}
-    cases = list(CASES) + [INT3_MATVEC_CASE]
-    for bits, sparse, n, s, m, g, seed in cases:
-        p = oracle.make_problem(bits, n, s, m, g, sparse=sparse, seed=seed)
+    cases = [c + (False,) for c in list(CASES) + [INT3_MATVEC_CASE]] + [c + (True,) for c in EXPONENT_CASES]
+    for bits, sparse, n, s, m, g, seed, expo in cases:
+        p = oracle.make_problem(bits, n, s, m, g, sparse=sparse, seed=seed, exponent_frac=0.5 if expo else 0.0)
         t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)
-        tag = f"b{bits}_{'sp' if sparse else 'dn'}_n{n}_s{s}_m{m}_g{g}_seed{seed}"
+        tag = f"b{bits}_{'sp' if sparse else 'dn'}_n{n}_s{s}_m{m}_g{g}_seed{seed}" + ("_exp" if expo else "")
         if sparse:
             # the packer: uint8 (S, N) weights and mask -> compacted words + bit mask
             wt = torch.empty((n // 16, s), dtype=torch.int32, device=dev)
