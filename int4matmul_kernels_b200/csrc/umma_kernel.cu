@@ -22,8 +22,6 @@
 
 #include <cuda.h>
 #include <dlfcn.h>
-#include <cstdio>
-#include <cstdlib>
 
 #include "common.cuh"
 #include "ptx.cuh"
