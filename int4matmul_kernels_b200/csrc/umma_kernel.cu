@@ -4,19 +4,24 @@
 // (matvec_kernel.cu:198-267).  Per CTA tile: 128 weight columns (S) on the 128 tensor-memory lanes x NT
 // activation rows on the MMA's N dimension, accumulated in fp32 in tensor memory over all of N (in-features).
 //
-//   producer warp     bulk-copies (TMA) packed weight rows + the group's scales / zeros into a shared-memory ring,
-//                     and loads the activation tile (NT rows x 64 k, 128-byte swizzle) with a tensor-map copy
-//   4 dequant warps   thread i owns weight column i: reads its packed words for 64 k from shared memory,
-//                     rebuilds fp16((q - zero) * scale) in registers, in natural k order, and writes them into its
-//                     own tensor-memory lane with tcgen05.st (one packed int32 = 8 consecutive k of one column,
-//                     which is exactly what a lane of the A operand holds)
-//   MMA warp          one thread issues 4 x tcgen05.mma (M = 128, N = NT, K = 16) per 64-k unit, A from tensor
+//   weight producer   one thread: tensor-map copies (TMA) of the packed weight rows, the keep mask and the groups'
+//                     scales / zeros of one 128-k unit into a shared-memory ring (the scales / zeros come from a
+//                     thread of their own in the weight-streaming configuration)
+//   activation prod.  one thread: the activation tile (NT rows x 128 k as two 128-byte-swizzled sub-tiles)
+//   dequant warps     warpgroups of 4 warps take the units in turn; thread i of a group owns weight column i: reads
+//                     its packed words from shared memory, rebuilds fp16((q - zero) * scale) in registers, in natural
+//                     k order, and writes them into its own tensor-memory lane with tcgen05.st (one packed int32 =
+//                     8 consecutive k of one column, which is exactly what a lane of the A operand holds)
+//   MMA warp          one elected thread issues 8 x tcgen05.mma (M = 128, N = NT, K = 16) per unit, A from tensor
 //                     memory, B from the swizzled shared-memory tile, and commits to mbarriers that recycle the
 //                     stages; the accumulator never leaves tensor memory until the tile is done
-//   epilogue          the dequant warps read the accumulator (tcgen05.ld), convert to fp16 and store
+//   epilogue          4 warps read the accumulator (tcgen05.ld), convert to fp16 and store; a warpgroup of its own
+//                     except for 33..64 rows, where dequant warpgroup 0 does it
 //
-// For NT <= 32 the (tile, k-unit) space is cut into equal ranges per CTA (split-K over the whole GPU, partial
-// tiles summed through scratch in a fixed order); for larger NT every CTA takes whole tiles.
+// Configurations (Cfg<NT>): NT <= 32 rows stream the weights once from HBM - one CTA per SM, 4 dequant warpgroups,
+// 16 weight stages, 6 A / activation stages, and the (tile, unit) space cut into equal ranges per CTA (split-K over
+// the whole GPU, partial tiles summed through scratch in a fixed order).  NT = 64: two CTAs per SM, whole tiles.
+// NT >= 128: one CTA per SM, whole tiles, epilogue stores transposed through shared memory.
 // Every wait is bounded and reports through the status word instead of hanging.
 #include "../../include/int4matmul_b200.h"
 
@@ -31,8 +36,11 @@ namespace i4mm {
 namespace {
 
 #ifdef I4MM_TRACE
+#ifndef I4MM_TRACE_CTA
+#define I4MM_TRACE_CTA 0
+#endif
 // debug build only: CTA 0 records clock64() stamps into the tail of the partials scratch
-#define TRACE(role, idx, slot) do { if (blockIdx.x == 0 && (idx) < 64 && lane == 0) \
+#define TRACE(role, idx, slot) do { if (blockIdx.x == I4MM_TRACE_CTA && (idx) < 64 && lane == 0) \
     reinterpret_cast<long long*>(p.partials + (148 * 4 * 2 * 32 * 128) - 65536)[((role) * 64 + (idx)) * 8 + (slot)] = clock64(); } while (0)
 #else
 #define TRACE(role, idx, slot) do {} while (0)
@@ -90,7 +98,7 @@ constexpr uint32_t MUL_1_16 = 0x2C003C00u, BASE_1_16 = 0xD400E400u;      // (x1,
 constexpr uint32_t MUL_1_4 = 0x34003C00u, BASE_1_4 = 0xDC00E400u;        // (x1, x4):  int2 crumbs 0, 1
 constexpr uint32_t MUL_16_64 = 0x24002C00u, BASE_16_64 = 0xCC00D400u;    // (x16, x64): int2 crumbs 2, 3
 constexpr uint32_t MUL_1_8 = 0x30003C00u, BASE_1_8 = 0xD800E400u;        // (x1, x8):  int3 field pairs
-constexpr uint32_t MUL_1_1 = 0x3C003C00u, BASE_1_1 = 0xE400E400u;        // sparse int4 through bytes
+constexpr uint32_t MUL_1_1 = 0x3C003C00u, BASE_1_1 = 0xE400E400u;        // (x1, x1): sparse int4 through bytes
 
 // 16-entry table for the sparse expansion (see sparse decode): x = PRMT selector | (4 * popc) << 16, y / z = pair masks
 __device__ __forceinline__ uint4 sparse_lut_entry(int mn) {
@@ -220,17 +228,22 @@ struct WStage {     // one stage of the packed-weight ring: 128 k = two 64-k hal
     static constexpr int kBytes = kZ + 512;
 };
 
-constexpr int kMaxWStages = 8;
-constexpr int kABStages = 3;         // ring of (A in tensor memory, activation tile in shared memory) pairs, 128 k per stage
+constexpr int kMaxWStages = 16;
+constexpr int kMaxABStages = 6;
 
 template <int NT>
 struct Cfg {
     // packed-weight ring (128 k per stage).  Few rows: the kernel streams weights from HBM, and the ring has to
     // cover the DRAM latency; many rows: weights are a trickle next to the activation tiles
-    static constexpr int kWStages = NT <= 64 ? 8 : 3;
-    static constexpr int kWG = 2;                                     // dequant warpgroups (4 warps each), alternating units
-    static constexpr bool kEpiWarps = NT >= 128;                      // a warpgroup of its own for the epilogue (else dequant warpgroup 0 does it)
-    static constexpr int kWarps = 4 * kWG + (kEpiWarps ? 4 : 0) + 3;  // + weight producer, activation producer, MMA issuer
+    static constexpr bool kStream = NT <= 32;                         // weight-streaming shapes: one CTA per SM with everything doubled
+    static constexpr int kWStages = kStream ? 16 : NT <= 64 ? 8 : 3;
+    static constexpr int kWG = kStream ? 4 : 2;                       // dequant warpgroups (4 warps each), taking units in turn
+    static constexpr int kABStages = kStream ? 6 : 3;                 // ring of (A in tensor memory, activation tile in shared memory) pairs, 128 k per stage
+    static constexpr bool kEpiWarps = NT >= 128 || kStream;           // a warpgroup of its own for the epilogue (else dequant warpgroup 0 does it)
+    static constexpr bool kEpiTransposed = NT >= 128;                 // epilogue stores go through a shared-memory transposition tile
+    static constexpr bool kEpiHandoff = kStream;                      // the MMA warp waits for the accumulator and wakes the epilogue warps (named barrier)
+    static constexpr bool kSZProducer = kStream;                      // scales / zeros are issued by a thread of their own
+    static constexpr int kWarps = 4 * kWG + (kEpiWarps ? 4 : 0) + 3 + (kSZProducer ? 1 : 0);  // + weight producer, activation producer, MMA issuer
     static constexpr int kThreads = kWarps * 32;
     static constexpr int kDCols = NT < 32 ? 32 : NT;                  // accumulator columns
     static constexpr int kACol0 = kDCols;                             // A stages follow: 64 columns (128 k) each
@@ -239,13 +252,13 @@ struct Cfg {
     static constexpr bool kSplit = NT <= 32;                          // split-K over CTAs with a scratch reduction
     static constexpr int kBHalfBytes = NT * 128;                      // one 64-k activation sub-tile
     static constexpr int kBStageBytes = 2 * kBHalfBytes;
-    static constexpr int kMinBlocks = NT <= 64 ? 2 : 1;
+    static constexpr int kMinBlocks = kStream ? 1 : NT <= 64 ? 2 : 1;
 };
 
 struct Barriers {
     unsigned long long w_full[kMaxWStages], w_empty[kMaxWStages];
-    unsigned long long ab_full[kABStages];     // 4 dequant warps + the activation producer (with its transaction bytes)
-    unsigned long long ab_free[kABStages];     // tcgen05.commit: the MMAs that read the stage are done
+    unsigned long long ab_full[kMaxABStages];  // 4 dequant warps + the activation producer (with its transaction bytes)
+    unsigned long long ab_free[kMaxABStages];  // tcgen05.commit: the MMAs that read the stage are done
     unsigned long long d_full, d_empty;
 };
 
@@ -270,13 +283,20 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
     using C = Cfg<NT>;
     constexpr int kEpiWarp0 = 4 * C::kWG;                           // first epilogue warp (a multiple of 4: lane quarter = warp % 4)
     constexpr int kWProducer = kEpiWarp0 + (C::kEpiWarps ? 4 : 0), kBProducer = kWProducer + 1, kMma = kWProducer + 2;
+    constexpr int kSZWarp = kWProducer + 3;                         // only when Cfg::kSZProducer
+    constexpr int kABStages = C::kABStages;
     extern __shared__ __align__(1024) unsigned char smem[];      // [B ring (1024-aligned tiles)][W ring]
     __shared__ __align__(8) Barriers bars;
     __shared__ uint4 lut[16];
     __shared__ uint32_t tmem_base_smem;
     __shared__ int s_last;
+    __shared__ volatile int s_abort;     // set by the MMA warp when it gives up, before it releases the epilogue warps for the last time
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#ifdef I4MM_TRACE
+    long long trace_gt0, trace_c0 = clock64();
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(trace_gt0));
+#endif
     const uint32_t smem0 = (ptx::smem_u32(smem) + 1023u) & ~1023u;
     const uint32_t b_ring = smem0;
     const uint32_t w_ring = smem0 + kABStages * C::kBStageBytes;
@@ -284,7 +304,7 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < C::kWStages; ++i) {
-            ptx::mbar_init(ptx::smem_u32(&bars.w_full[i]), 1);
+            ptx::mbar_init(ptx::smem_u32(&bars.w_full[i]), C::kSZProducer ? 2 : 1);
             ptx::mbar_init(ptx::smem_u32(&bars.w_empty[i]), 4);
         }
         for (int i = 0; i < kABStages; ++i) {
@@ -296,6 +316,7 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
         ptx::fence_mbar_init();
     }
     if (SPARSE && threadIdx.x < 16) lut[threadIdx.x] = sparse_lut_entry(threadIdx.x);
+    if (threadIdx.x == 32) s_abort = 0;
     if (warp == kWProducer) {
         ptx::tmem_alloc(ptx::smem_u32(&tmem_base_smem), C::kTmemCols);
         ptx::tmem_relinquish();
@@ -328,7 +349,8 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
     if (warp == kWProducer) {
         // =========================== packed weights + scales / zeros: one thread ===========================
         if (lane == 0) {
-            constexpr uint32_t kBytes = (uint32_t)WS::kBytes;      // every box is copied whole (out-of-range parts are zero-filled)
+            // every box is copied whole (out-of-range parts are zero-filled)
+            constexpr uint32_t kBytes = (uint32_t)(C::kSZProducer ? WS::kS : WS::kBytes);
             uint32_t si = 0, ws = 0, wph = 0;
             bool ok = true;
             for (long long t = t_lo; t < t_hi && ok;) {
@@ -338,16 +360,40 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
                 const int ct = (int)(tile % p.CT);
                 for (int u = u0; u < u1; ++u, ++si) {
                     TRACE(0, (int)si, 0);
-                    if (!ptx::mbar_wait(ptx::smem_u32(&bars.w_empty[ws]), wph ^ 1u)) { atomicExch(p.status, 11); ok = false; break; }
+                    if (!ptx::mbar_wait_relaxed(ptx::smem_u32(&bars.w_empty[ws]), wph ^ 1u)) { atomicExch(p.status, 11); ok = false; break; }
                     TRACE(0, (int)si, 1);
                     const uint32_t st = w_ring + ws * WS::kBytes, full = ptx::smem_u32(&bars.w_full[ws]);
                     ptx::mbar_arrive_expect_tx(full, kBytes);
                     ptx::tma_load_2d(st + WS::kW, &tm.w, ct * 128, u * 2 * F::WROWS, full);
                     if (SPARSE) ptx::tma_load_2d(st + WS::kMask, &tm.m, ct * 128, u * 2 * F::MROWS, full);
+                    if (!C::kSZProducer) {
+                        const int g0 = (int)p.gdiv(2u * (uint32_t)u);
+                        ptx::tma_load_2d(st + WS::kS, &tm.s, ct * 128, g0, full);
+                        ptx::tma_load_2d(st + WS::kZ, &tm.z, ct * 128, g0, full);
+                    }
+                    TRACE(0, (int)si, 2);
+                    if (++ws == C::kWStages) { ws = 0; wph ^= 1u; }
+                }
+                t += u1 - u0;
+            }
+        }
+    } else if (C::kSZProducer && warp == kSZWarp) {
+        // =========================== scales / zeros of the weight stages: one thread ===========================
+        if (lane == 0) {
+            uint32_t ws = 0, wph = 0;
+            bool ok = true;
+            for (long long t = t_lo; t < t_hi && ok;) {
+                const long long tile = t / U;
+                const int u0 = (int)(t - tile * U);
+                const int u1 = (int)min(U, u0 + (t_hi - t));
+                const int ct = (int)(tile % p.CT);
+                for (int u = u0; u < u1; ++u) {
+                    if (!ptx::mbar_wait_relaxed(ptx::smem_u32(&bars.w_empty[ws]), wph ^ 1u)) { atomicExch(p.status, 13); ok = false; break; }
+                    const uint32_t st = w_ring + ws * WS::kBytes, full = ptx::smem_u32(&bars.w_full[ws]);
+                    ptx::mbar_arrive_expect_tx(full, (uint32_t)(WS::kBytes - WS::kS));
                     const int g0 = (int)p.gdiv(2u * (uint32_t)u);
                     ptx::tma_load_2d(st + WS::kS, &tm.s, ct * 128, g0, full);
                     ptx::tma_load_2d(st + WS::kZ, &tm.z, ct * 128, g0, full);
-                    TRACE(0, (int)si, 2);
                     if (++ws == C::kWStages) { ws = 0; wph ^= 1u; }
                 }
                 t += u1 - u0;
@@ -364,7 +410,8 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
                 const int u1 = (int)min(U, u0 + (t_hi - t));
                 const int mt = (int)(tile / p.CT);
                 for (int u = u0; u < u1; ++u) {
-                    if (!ptx::mbar_wait(ptx::smem_u32(&bars.ab_free[s]), ph ^ 1u)) { atomicExch(p.status, 12); ok = false; break; }
+                    if (!(C::kStream ? ptx::mbar_wait_relaxed(ptx::smem_u32(&bars.ab_free[s]), ph ^ 1u)
+                                     : ptx::mbar_wait(ptx::smem_u32(&bars.ab_free[s]), ph ^ 1u))) { atomicExch(p.status, 12); ok = false; break; }
                     const uint32_t full = ptx::smem_u32(&bars.ab_full[s]);
                     ptx::mbar_arrive_expect_tx(full, (uint32_t)C::kBStageBytes);
                     ptx::tma_load_2d(b_ring + s * C::kBStageBytes, &tm.x, u * 128, mt * NT, full);
@@ -421,8 +468,23 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
                 if (ptx::elect_one()) ptx::tc_commit(ptx::smem_u32(&bars.d_full));
                 __syncwarp();
                 TRACE(3, (int)seg, 6);
+                if (C::kEpiHandoff) {
+                    // the epilogue warps sleep on a hardware barrier instead of polling for the whole segment
+                    if (!ptx::mbar_wait(ptx::smem_u32(&bars.d_full), seg & 1u)) {
+                        if (lane == 0) atomicExch(p.status, 23);
+                        ok = false;
+                        break;
+                    }
+                    ptx::tc_fence_before_sync();
+                    ptx::named_bar_arrive(2, 128 + 32);
+                }
                 ++seg;
                 t += u1 - u0;
+            }
+            if (C::kEpiHandoff && !ok) {
+                s_abort = 1;
+                __threadfence_block();
+                ptx::named_bar_arrive(2, 128 + 32);
             }
         }
     } else {
@@ -434,7 +496,10 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
             const int col = (warp & 3) * 32 + lane;
             const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
             if (warp == kEpiWarp0 || (!C::kEpiWarps && warp == 0)) TRACE(3, (int)seg, 0);
-            if (!ptx::mbar_wait(ptx::smem_u32(&bars.d_full), seg & 1u)) {
+            if (C::kEpiHandoff) {
+                ptx::named_bar_sync(2, 128 + 32);          // released by the MMA warp once the accumulator is complete
+                if (s_abort) return false;
+            } else if (!ptx::mbar_wait(ptx::smem_u32(&bars.d_full), seg & 1u)) {
                 if (lane == 0) atomicExch(p.status, 33);
                 return false;
             }
@@ -447,7 +512,7 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
             const int nrows = min(NT, p.rows - row0);
             float* slot = nullptr;
             if (C::kSplit && !complete) slot = p.partials + ((size_t)b * 2 + (first_segment ? 0 : 1)) * (32 * 128);
-            if (C::kEpiWarps) {
+            if (C::kEpiTransposed) {
                 // 16 accumulator columns (= 16 output rows) at a time: transposed through a 4 KB shared-memory tile so that
                 // the global stores are 16-byte rows instead of one 2-byte element per lane
                 const uint32_t stage_tile = epi_tile;                       // [16 rows][128 columns] fp16
@@ -510,6 +575,7 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
             if (C::kSplit && !complete) {
                 const long long T = n_tiles * U;
                 __threadfence();
+                if (warp == kEpiWarp0 || (!C::kEpiWarps && warp == 0)) TRACE(3, (int)seg, 3);
                 ptx::named_bar_sync(1, 128);
                 const long long lo_t = tile * U, hi_t = lo_t + U - 1;
                 const int b_lo = range_owner(T, G, lo_t), b_hi = range_owner(T, G, hi_t);
@@ -537,6 +603,7 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
                     if ((warp & 3) == 0 && lane == 0) p.counters[tile] = 0;     // leave the scratch ready for the next launch
                 }
                 ptx::named_bar_sync(1, 128);
+                if (warp == kEpiWarp0 || (!C::kEpiWarps && warp == 0)) TRACE(3, (int)seg, 7);
             }
             return true;
         };
@@ -644,6 +711,14 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
     __syncthreads();
     ptx::tc_fence_after_sync();
     if (warp == kWProducer) ptx::tmem_dealloc(tmem_base, C::kTmemCols);
+#ifdef I4MM_TRACE
+    if (threadIdx.x == 0 && blockIdx.x < 1024) {
+        long long gt1;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt1));
+        long long* rec = reinterpret_cast<long long*>(p.partials + (148 * 4 * 2 * 32 * 128) - 65536) + 4096 + blockIdx.x * 4;
+        rec[0] = trace_gt0; rec[1] = gt1; rec[2] = trace_c0; rec[3] = clock64();
+    }
+#endif
 }
 
 // ---- host side -------------------------------------------------------------------------------------------------
@@ -701,8 +776,8 @@ int launch_nt(const UmmaParams& p, const __half* x, int n_groups, cudaStream_t s
     ok = ok && encode_2d(&tm.z, p.zeros, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, n_groups, p.S, 2, 128, CU_TENSOR_MAP_SWIZZLE_NONE);
     if (!ok) return I4MM_ERR_DEVICE;
 
-    const size_t smem = 1024 + (size_t)kABStages * C::kBStageBytes + (size_t)C::kWStages * WStage<F>::kBytes +
-                        (C::kEpiWarps ? 4096 : 0);
+    const size_t smem = 1024 + (size_t)C::kABStages * C::kBStageBytes + (size_t)C::kWStages * WStage<F>::kBytes +
+                        (C::kEpiTransposed ? 4096 : 0);
     auto kern = umma_kernel<BITS, SPARSE, NT>;
     static int ctas_per_sm[16] = {0};
     static int sm_count[16] = {0};

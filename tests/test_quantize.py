@@ -58,7 +58,8 @@ def test_quant_linear_module(bits, sparse):
         xs = x.reshape(1, -1, 512).cpu().numpy()
         want = oracle.matmul_ref(xs, w16)
         assert_parity(y.reshape(1, -1, 256).cpu().numpy(), want, oracle.matmul_abs_bound(xs, w16), "QuantLinear")
-    # and the quantised layer stays close to the float layer
+    # and the quantised layer stays close to the float layer: rounding to 2^bits levels over ~5 sigma of a group gives a
+    # mean |error| of about 0.8 * sqrt(512) * 5 * 0.03 / ((2^bits - 1) * sqrt(12)) = 0.05 / 0.11 / 0.26 for 4 / 3 / 2 bits
     xf = torch.randn((8, 512), generator=gen)
     err = (lin(xf.to(torch.float16).cuda()).float().cpu() - xf @ (w if not sparse else w * qz["keep"].t().float())).abs().mean()
-    assert err < {4: 0.05, 3: 0.1, 2: 0.25}[bits]
+    assert err < {4: 0.08, 3: 0.16, 2: 0.4}[bits]
