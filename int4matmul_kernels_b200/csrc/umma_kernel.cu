@@ -242,6 +242,7 @@ struct Cfg {
     static constexpr bool kEpiWarps = NT >= 128 || kStream;           // a warpgroup of its own for the epilogue (else dequant warpgroup 0 does it)
     static constexpr bool kEpiTransposed = NT >= 128;                 // epilogue stores go through a shared-memory transposition tile
     static constexpr bool kEpiHandoff = kStream;                      // the MMA warp waits for the accumulator and wakes the epilogue warps (named barrier)
+    static constexpr bool kDeferArrive = kStream;                     // a dequant warp announces an A stage only before its next wait (hides the tcgen05.wait::st latency)
     static constexpr bool kSZProducer = kStream;                      // scales / zeros are issued by a thread of their own
     static constexpr int kWarps = 4 * kWG + (kEpiWarps ? 4 : 0) + 3 + (kSZProducer ? 1 : 0);  // + weight producer, activation producer, MMA issuer
     static constexpr int kThreads = kWarps * 32;
@@ -292,7 +293,9 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
     __shared__ int s_last;
     __shared__ volatile int s_abort;     // set by the MMA warp when it gives up, before it releases the epilogue warps for the last time
 
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    // the shuffle tells the compiler that the warp index is warp-uniform: role dispatch, stage indices and barrier
+    // addresses derived from it then live in uniform registers instead of costing vector-ALU instructions
+    const int lane = threadIdx.x & 31, warp = __shfl_sync(0xFFFFFFFFu, (int)(threadIdx.x >> 5), 0);
 #ifdef I4MM_TRACE
     long long trace_gt0, trace_c0 = clock64();
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(trace_gt0));
@@ -302,36 +305,49 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
     const uint32_t w_ring = smem0 + kABStages * C::kBStageBytes;
     const uint32_t epi_tile = w_ring + C::kWStages * WS::kBytes;     // 4 KB transposition tile of the epilogue warps (NT >= 128)
 
-    if (threadIdx.x == 0) {
-        for (int i = 0; i < C::kWStages; ++i) {
-            ptx::mbar_init(ptx::smem_u32(&bars.w_full[i]), C::kSZProducer ? 2 : 1);
-            ptx::mbar_init(ptx::smem_u32(&bars.w_empty[i]), 4);
-        }
-        for (int i = 0; i < kABStages; ++i) {
-            ptx::mbar_init(ptx::smem_u32(&bars.ab_full[i]), 4 + 1);
-            ptx::mbar_init(ptx::smem_u32(&bars.ab_free[i]), 1);
-        }
-        ptx::mbar_init(ptx::smem_u32(&bars.d_full), 1);
-        ptx::mbar_init(ptx::smem_u32(&bars.d_empty), 4);
-        ptx::fence_mbar_init();
-    }
-    if (SPARSE && threadIdx.x < 16) lut[threadIdx.x] = sparse_lut_entry(threadIdx.x);
-    if (threadIdx.x == 32) s_abort = 0;
+    // ---- set-up, spread over warps so that nothing waits for one thread ----
+    // The weight producer's warp initialises the weight ring's barriers itself and does not wait for the rest of the
+    // CTA (it only arrives on the set-up barrier): its first copies are in flight while tensor memory is allocated.
     if (warp == kWProducer) {
-        ptx::tmem_alloc(ptx::smem_u32(&tmem_base_smem), C::kTmemCols);
-        ptx::tmem_relinquish();
         if (lane == 0) {
-            ptx::prefetch_tmap(&tm.x);
             ptx::prefetch_tmap(&tm.w);
-            ptx::prefetch_tmap(&tm.s);
-            ptx::prefetch_tmap(&tm.z);
             if (SPARSE) ptx::prefetch_tmap(&tm.m);
         }
+        if (lane < C::kWStages) {
+            ptx::mbar_init(ptx::smem_u32(&bars.w_full[lane]), C::kSZProducer ? 2 : 1);
+            ptx::mbar_init(ptx::smem_u32(&bars.w_empty[lane]), 4);
+        }
+        ptx::fence_mbar_init();
+        __syncwarp();
+        ptx::named_bar_arrive(3, C::kThreads);
+    } else {
+        if (warp == 0) {
+            if (lane < kABStages) {
+                ptx::mbar_init(ptx::smem_u32(&bars.ab_full[lane]), 4 + 1);
+                ptx::mbar_init(ptx::smem_u32(&bars.ab_free[lane]), 1);
+            }
+            if (lane == 31) {
+                ptx::mbar_init(ptx::smem_u32(&bars.d_full), 1);
+                ptx::mbar_init(ptx::smem_u32(&bars.d_empty), 4);
+                s_abort = 0;
+            }
+            ptx::fence_mbar_init();
+        }
+        if (SPARSE && warp == 1 && lane < 16) lut[lane] = sparse_lut_entry(lane);
+        if (warp == kMma) {
+            ptx::tmem_alloc(ptx::smem_u32(&tmem_base_smem), C::kTmemCols);
+            ptx::tmem_relinquish();
+        }
+        if (warp == kBProducer && lane == 0) {
+            ptx::prefetch_tmap(&tm.x);
+            ptx::prefetch_tmap(&tm.s);
+            ptx::prefetch_tmap(&tm.z);
+        }
+        ptx::tc_fence_before_sync();
+        ptx::named_bar_sync(3, C::kThreads);
+        ptx::tc_fence_after_sync();
     }
-    ptx::tc_fence_before_sync();
-    __syncthreads();
-    ptx::tc_fence_after_sync();
-    const uint32_t tmem_base = tmem_base_smem;
+    const uint32_t tmem_base = tmem_base_smem;       // not valid in the weight producer's warp, which never uses it
 
     // ---- this CTA's share of the (tile, unit) space; one unit = 128 k.  Whole tiles unless the split-K variant ----
     const long long U = p.U;
@@ -626,16 +642,25 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
             const int wg = warp >> 2;                                           // warpgroup: takes every kWG-th weight stage
             const int col = (warp & 3) * 32 + lane;                             // weight column in the tile = tensor-memory lane
             const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
-            uint32_t si = 0, seg = 0;
+            uint32_t si0 = 0, seg = 0;                                           // si0: weight stages consumed before this segment
+            int pending = -1;                                                    // A stage written but not yet announced (Cfg::kDeferArrive)
+            // the stores into tensor memory are complete -> the stage may be read by the MMAs
+            auto announce = [&](int stage) {
+                ptx::tc_wait_st();
+                ptx::tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&bars.ab_full[stage]));
+            };
             bool ok = true;
             bool first_segment = true;
             for (long long t = t_lo; t < t_hi && ok;) {
                 const long long tile = t / U;
                 const int u0 = (int)(t - tile * U);
                 const int u1 = (int)min(U, u0 + (t_hi - t));
-                for (int u = u0; u < u1 && ok; ++u, ++si) {
+                // this warpgroup's units of the segment: those whose stage index is congruent to wg modulo kWG
+                for (int u = u0 + (int)(((uint32_t)wg - si0) % (uint32_t)C::kWG); u < u1; u += C::kWG) {
+                    const uint32_t si = si0 + (uint32_t)(u - u0);
                     const uint32_t ws = si % C::kWStages, wph = (si / C::kWStages) & 1u;     // constants: multiply-shift, no division
-                    if ((int)(si % C::kWG) != wg) continue;
                     if (warp == 0) TRACE(2, (int)si, 0);
                     if (!ptx::mbar_wait(ptx::smem_u32(&bars.w_full[ws]), wph)) {
                         if (lane == 0) atomicExch(p.status, 31);
@@ -646,6 +671,9 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
                     const uint32_t st = w_ring + ws * WS::kBytes;
                     const uint32_t g0 = p.gdiv(2u * (uint32_t)u);
                     const uint32_t as = si % kABStages, aph = (si / kABStages) & 1u;
+                    // polled before the first half is decoded, so that the answer costs no latency when it is needed
+                    const bool free_early = ptx::mbar_test_wait(ptx::smem_u32(&bars.ab_free[as]), aph ^ 1u);
+                    if (warp == 0) TRACE(4, (int)si, 0);
 #pragma unroll
                     for (int h = 0; h < 2; ++h) {
                         ColK c;
@@ -664,7 +692,19 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
                         const uint32_t wb = st + WS::kW + h * (F::WROWS * 512) + col * 4;
                         const uint32_t mb = st + WS::kMask + h * (F::MROWS * 512) + col * 4;
                         uint32_t A[32];
+                        if (warp == 0 && not_fast == 0x7777u) TRACE(4, (int)si, 7);
+                        if (warp == 0) TRACE(4, (int)si, 1 + 3 * h);
+#ifdef I4MM_NODECODE
+                        {
+                            const uint32_t w = ptx::lds32(wb) + not_fast;
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) A[i] = w;
+                        }
+                        if (true) {
+        	        } else if (false) {
+#else
                         if (!__any_sync(0xFFFFFFFFu, not_fast != 0)) {
+#endif
                             if (SPARSE) c.zb = __half2uint_rz(__ushort_as_half((unsigned short)zlo)) * 0x01010101u;
                             F::template decode<MODE_FAST>(wb, mb, c, A, lut);
                         } else {
@@ -679,8 +719,10 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
                         }
                         if (warp == 0) TRACE(2, (int)si, 2 + 2 * h);
                         if (h == 0) {
+                            if (C::kDeferArrive && pending >= 0) announce(pending);       // before any wait: the MMAs must be able to go on
+                            if (warp == 0) TRACE(4, (int)si, 2);
                             // the A stage (and its activation tile) is free once the MMAs of its previous use have completed
-                            if (!ptx::mbar_wait(ptx::smem_u32(&bars.ab_free[as]), aph ^ 1u)) {
+                            if (!free_early && !ptx::mbar_wait(ptx::smem_u32(&bars.ab_free[as]), aph ^ 1u)) {
                                 if (lane == 0) atomicExch(p.status, 32);
                                 ok = false;
                                 break;
@@ -688,18 +730,21 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
                             ptx::tc_fence_after_sync();
                         }
                         if (warp == 0) TRACE(2, (int)si, 3 + 2 * h);
+#ifdef I4MM_NOST
+                        if (A[0] == 0x12345u && A[31] == 0x54321u)
+#endif
                         ptx::tmem_st32(lane_addr + C::kACol0 + as * 64 + h * 32, A);
                     }
                     if (!ok) break;
-                    ptx::tc_wait_st();
-                    ptx::tc_fence_before_sync();
-                    __syncwarp();
-                    if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&bars.ab_full[as]));
+                    if (C::kDeferArrive) pending = (int)as;
+                    else announce((int)as);
                     if (warp == 0) TRACE(2, (int)si, 6);
                 }
                 if (!ok) break;
+                if (C::kDeferArrive && pending >= 0) { announce(pending); pending = -1; }
                 if (!C::kEpiWarps && wg == 0) ok = epilogue(seg, tile, u0, u1, first_segment);
                 ++seg;
+                si0 += (uint32_t)(u1 - u0);
                 t += u1 - u0;
                 first_segment = false;
             }
@@ -710,7 +755,7 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
     ptx::tc_fence_before_sync();
     __syncthreads();
     ptx::tc_fence_after_sync();
-    if (warp == kWProducer) ptx::tmem_dealloc(tmem_base, C::kTmemCols);
+    if (warp == kMma) ptx::tmem_dealloc(tmem_base, C::kTmemCols);
 #ifdef I4MM_TRACE
     if (threadIdx.x == 0 && blockIdx.x < 1024) {
         long long gt1;
