@@ -44,7 +44,8 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
 }
 
 // Bounded wait for roles that run far ahead of their consumers (ring producers): a non-blocking test and a
-// sleep between polls, so that a blocked producer costs next to no issue slots.  2^18 polls of >= 200 ns each.
+// sleep between polls that doubles from 100 ns up to max_sleep_ns, so that a blocked producer costs next to no
+// issue slots.  max_sleep_ns must stay well below the time the ring takes to drain.
 __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
@@ -54,10 +55,12 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
         : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
-__device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity, uint32_t max_sleep_ns) {
+    uint32_t ns = 100;
     for (uint32_t i = 0; i < kSpinLimit; ++i) {
         if (mbar_test_wait(bar, parity)) return true;
-        __nanosleep(200);
+        __nanosleep(ns);
+        if (ns < max_sleep_ns) ns *= 2;
     }
     return false;
 }
@@ -95,6 +98,16 @@ __device__ __forceinline__ void named_bar_arrive(uint32_t id, uint32_t threads) 
 }
 __device__ __forceinline__ void named_bar_sync(uint32_t id, uint32_t threads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+// ---- 64-bit global accesses that other CTAs may race with (single-copy atomic, device scope) ---------------
+__device__ __forceinline__ unsigned long long ld_relaxed_gpu_u64(const unsigned long long* p) {
+    unsigned long long v;
+    asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_relaxed_gpu_u64(unsigned long long* p, unsigned long long v) {
+    asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
 
 // ---- shared-memory loads by 32-bit shared address -------------------------------------------------------

@@ -56,7 +56,6 @@ struct UmmaParams {
     const __half* scales;
     const __half* zeros;
     float* partials;
-    unsigned int* counters;
     int* status;
     int rows;            // all activation rows (B * M)
     int N, S;
@@ -290,7 +289,6 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
     __shared__ __align__(8) Barriers bars;
     __shared__ uint4 lut[16];
     __shared__ uint32_t tmem_base_smem;
-    __shared__ int s_last;
     __shared__ volatile int s_abort;     // set by the MMA warp when it gives up, before it releases the epilogue warps for the last time
 
     // the shuffle tells the compiler that the warp index is warp-uniform: role dispatch, stage indices and barrier
@@ -376,7 +374,7 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
                 const int ct = (int)(tile % p.CT);
                 for (int u = u0; u < u1; ++u, ++si) {
                     TRACE(0, (int)si, 0);
-                    if (!ptx::mbar_wait_relaxed(ptx::smem_u32(&bars.w_empty[ws]), wph ^ 1u)) { atomicExch(p.status, 11); ok = false; break; }
+                    if (!ptx::mbar_wait_relaxed(ptx::smem_u32(&bars.w_empty[ws]), wph ^ 1u, 1600)) { atomicExch(p.status, 11); ok = false; break; }
                     TRACE(0, (int)si, 1);
                     const uint32_t st = w_ring + ws * WS::kBytes, full = ptx::smem_u32(&bars.w_full[ws]);
                     ptx::mbar_arrive_expect_tx(full, kBytes);
@@ -404,7 +402,7 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
                 const int u1 = (int)min(U, u0 + (t_hi - t));
                 const int ct = (int)(tile % p.CT);
                 for (int u = u0; u < u1; ++u) {
-                    if (!ptx::mbar_wait_relaxed(ptx::smem_u32(&bars.w_empty[ws]), wph ^ 1u)) { atomicExch(p.status, 13); ok = false; break; }
+                    if (!ptx::mbar_wait_relaxed(ptx::smem_u32(&bars.w_empty[ws]), wph ^ 1u, 1600)) { atomicExch(p.status, 13); ok = false; break; }
                     const uint32_t st = w_ring + ws * WS::kBytes, full = ptx::smem_u32(&bars.w_full[ws]);
                     ptx::mbar_arrive_expect_tx(full, (uint32_t)(WS::kBytes - WS::kS));
                     const int g0 = (int)p.gdiv(2u * (uint32_t)u);
@@ -426,7 +424,7 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
                 const int u1 = (int)min(U, u0 + (t_hi - t));
                 const int mt = (int)(tile / p.CT);
                 for (int u = u0; u < u1; ++u) {
-                    if (!(C::kStream ? ptx::mbar_wait_relaxed(ptx::smem_u32(&bars.ab_free[s]), ph ^ 1u)
+                    if (!(C::kStream ? ptx::mbar_wait_relaxed(ptx::smem_u32(&bars.ab_free[s]), ph ^ 1u, 400)
                                      : ptx::mbar_wait(ptx::smem_u32(&bars.ab_free[s]), ph ^ 1u))) { atomicExch(p.status, 12); ok = false; break; }
                     const uint32_t full = ptx::smem_u32(&bars.ab_full[s]);
                     ptx::mbar_arrive_expect_tx(full, (uint32_t)C::kBStageBytes);
@@ -526,8 +524,22 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
             const bool col_ok = scol < p.S;
             const int row0 = mt * NT;
             const int nrows = min(NT, p.rows - row0);
-            float* slot = nullptr;
-            if (C::kSplit && !complete) slot = p.partials + ((size_t)b * 2 + (first_segment ? 0 : 1)) * (32 * 128);
+            // Split-K: the CTAs b_lo .. b_hi share this tile.  b_lo (which owns the tile's first units and reaches them
+            // last) adds the others' partial tiles to its own accumulator in CTA order - a fixed order, so results are
+            // reproducible.  A partial element is one 64-bit word (fp32 value | tag 1 in the high half), written with a
+            // single store, so no fence, counter or second round trip is needed; the reader clears what it has read,
+            // which leaves the scratch all-zero for the next launch.  Every other CTA's share of the tile is the first
+            // segment of its range, so one slot per CTA is enough.
+            int b_lo = 0, b_hi = -1;
+            unsigned long long* slot = nullptr;
+            unsigned long long* const partials64 = reinterpret_cast<unsigned long long*>(p.partials);
+            if (C::kSplit && !complete) {
+                const long long T = n_tiles * U, lo_t = tile * U;
+                b_lo = range_owner(T, G, lo_t);
+                b_hi = range_owner(T, G, lo_t + U - 1);
+                if ((int)b != b_lo) slot = partials64 + (size_t)b * (32 * 128);
+            }
+            (void)first_segment;
             if (C::kEpiTransposed) {
                 // 16 accumulator columns (= 16 output rows) at a time: transposed through a 4 KB shared-memory tile so that
                 // the global stores are 16-byte rows instead of one 2-byte element per lane
@@ -559,7 +571,7 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
                     ptx::named_bar_sync(1, 128);
                 }
             } else {
-            constexpr int CH = NT >= 32 ? 32 : 16;          // accumulator columns per tensor-memory load
+            constexpr int CH = NT >= 64 ? 32 : 16;          // accumulator columns per tensor-memory load
 #pragma unroll 1
             for (int j0 = 0; j0 < NT; j0 += CH) {
                 uint32_t v[CH];
@@ -571,14 +583,48 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
                     __syncwarp();
                     if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&bars.d_empty));
                 }
+                if (slot) {
 #pragma unroll
-                for (int j = 0; j < CH; ++j) {
-                    const int m = j0 + j;
-                    if (m < nrows) {
-                        float f = __uint_as_float(v[j]);
-                        if (slot) {
-                            __stcg(slot + m * 128 + col, f);
-                        } else if (col_ok) {
+                    for (int j = 0; j < CH; ++j)
+                        if (j0 + j < nrows) ptx::st_relaxed_gpu_u64(slot + (j0 + j) * 128 + col, (1ull << 32) | v[j]);
+                    continue;
+                }
+                if (C::kSplit) {
+                    bool waiting_ok = true;
+                    for (int bb = b_lo + 1; bb <= b_hi; ++bb) {
+                        unsigned long long* src = partials64 + (size_t)bb * (32 * 128) + col;
+#pragma unroll
+                        for (int jb = 0; jb < CH; jb += 8) {
+                            if (j0 + jb >= nrows) break;                       // warp-uniform
+                            unsigned long long w[8];
+#pragma unroll
+                            for (int i = 0; i < 8; ++i)
+                                if (j0 + jb + i < nrows) w[i] = ptx::ld_relaxed_gpu_u64(src + (j0 + jb + i) * 128);
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) {
+                                if (j0 + jb + i < nrows) {
+                                    for (uint32_t spins = 0; (uint32_t)(w[i] >> 32) != 1u && waiting_ok; ++spins) {
+                                        if (spins >= ptx::kSpinLimit) {        // a contributor never delivered: report, stop waiting
+                                            atomicExch(p.status, 34);
+                                            waiting_ok = false;
+                                            break;
+                                        }
+                                        __nanosleep(64);
+                                        w[i] = ptx::ld_relaxed_gpu_u64(src + (j0 + jb + i) * 128);
+                                    }
+                                    v[jb + i] = __float_as_uint(__uint_as_float(v[jb + i]) + __uint_as_float((uint32_t)w[i]));
+                                    ptx::st_relaxed_gpu_u64(src + (j0 + jb + i) * 128, 0ull);
+                                }
+                            }
+                        }
+                    }
+                }
+                if (col_ok) {
+#pragma unroll
+                    for (int j = 0; j < CH; ++j) {
+                        const int m = j0 + j;
+                        if (m < nrows) {
+                            float f = __uint_as_float(v[j]);
                             __half* o = p.out + (size_t)(row0 + m) * p.S + scol;
                             if (p.accumulate) f += __half2float(*o);
                             *o = __float2half_rn(f);
@@ -588,39 +634,6 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
             }
             }
             if (warp == kEpiWarp0 || (!C::kEpiWarps && warp == 0)) TRACE(3, (int)seg, 2);
-            if (C::kSplit && !complete) {
-                const long long T = n_tiles * U;
-                __threadfence();
-                if (warp == kEpiWarp0 || (!C::kEpiWarps && warp == 0)) TRACE(3, (int)seg, 3);
-                ptx::named_bar_sync(1, 128);
-                const long long lo_t = tile * U, hi_t = lo_t + U - 1;
-                const int b_lo = range_owner(T, G, lo_t), b_hi = range_owner(T, G, hi_t);
-                if ((warp & 3) == 0 && lane == 0) {
-                    const unsigned int prev = atomicAdd(p.counters + tile, 1u);
-                    s_last = (prev == (unsigned int)(b_hi - b_lo)) ? 1 : 0;
-                }
-                ptx::named_bar_sync(1, 128);
-                if (s_last) {
-                    // the last CTA to arrive sums the partial tiles in CTA order: a fixed order, so results are reproducible
-                    __threadfence();
-                    const bool lo_starts_here = range_lo(T, G, b_lo) == lo_t;
-                    if (col_ok) {
-                        for (int m = 0; m < nrows; ++m) {
-                            float f = 0.f;
-                            for (int bb = b_lo; bb <= b_hi; ++bb) {
-                                const int which = (bb > b_lo || lo_starts_here) ? 0 : 1;
-                                f += __ldcg(p.partials + ((size_t)bb * 2 + which) * (32 * 128) + m * 128 + col);
-                            }
-                            __half* o = p.out + (size_t)(row0 + m) * p.S + scol;
-                            if (p.accumulate) f += __half2float(*o);
-                            *o = __float2half_rn(f);
-                        }
-                    }
-                    if ((warp & 3) == 0 && lane == 0) p.counters[tile] = 0;     // leave the scratch ready for the next launch
-                }
-                ptx::named_bar_sync(1, 128);
-                if (warp == kEpiWarp0 || (!C::kEpiWarps && warp == 0)) TRACE(3, (int)seg, 7);
-            }
             return true;
         };
 
@@ -658,7 +671,7 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
                 const int u0 = (int)(t - tile * U);
                 const int u1 = (int)min(U, u0 + (t_hi - t));
                 // this warpgroup's units of the segment: those whose stage index is congruent to wg modulo kWG
-                for (int u = u0 + (int)(((uint32_t)wg - si0) % (uint32_t)C::kWG); u < u1; u += C::kWG) {
+                for (int u = u0 + (int)(((uint32_t)wg + (uint32_t)C::kWG - si0 % (uint32_t)C::kWG) % (uint32_t)C::kWG); u < u1; u += C::kWG) {
                     const uint32_t si = si0 + (uint32_t)(u - u0);
                     const uint32_t ws = si % C::kWStages, wph = (si / C::kWStages) & 1u;     // constants: multiply-shift, no division
                     if (warp == 0) TRACE(2, (int)si, 0);
@@ -673,7 +686,6 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
                     const uint32_t as = si % kABStages, aph = (si / kABStages) & 1u;
                     // polled before the first half is decoded, so that the answer costs no latency when it is needed
                     const bool free_early = ptx::mbar_test_wait(ptx::smem_u32(&bars.ab_free[as]), aph ^ 1u);
-                    if (warp == 0) TRACE(4, (int)si, 0);
 #pragma unroll
                     for (int h = 0; h < 2; ++h) {
                         ColK c;
@@ -692,19 +704,7 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
                         const uint32_t wb = st + WS::kW + h * (F::WROWS * 512) + col * 4;
                         const uint32_t mb = st + WS::kMask + h * (F::MROWS * 512) + col * 4;
                         uint32_t A[32];
-                        if (warp == 0 && not_fast == 0x7777u) TRACE(4, (int)si, 7);
-                        if (warp == 0) TRACE(4, (int)si, 1 + 3 * h);
-#ifdef I4MM_NODECODE
-                        {
-                            const uint32_t w = ptx::lds32(wb) + not_fast;
-#pragma unroll
-                            for (int i = 0; i < 32; ++i) A[i] = w;
-                        }
-                        if (true) {
-        	        } else if (false) {
-#else
                         if (!__any_sync(0xFFFFFFFFu, not_fast != 0)) {
-#endif
                             if (SPARSE) c.zb = __half2uint_rz(__ushort_as_half((unsigned short)zlo)) * 0x01010101u;
                             F::template decode<MODE_FAST>(wb, mb, c, A, lut);
                         } else {
@@ -720,7 +720,6 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
                         if (warp == 0) TRACE(2, (int)si, 2 + 2 * h);
                         if (h == 0) {
                             if (C::kDeferArrive && pending >= 0) announce(pending);       // before any wait: the MMAs must be able to go on
-                            if (warp == 0) TRACE(4, (int)si, 2);
                             // the A stage (and its activation tile) is free once the MMAs of its previous use have completed
                             if (!free_early && !ptx::mbar_wait(ptx::smem_u32(&bars.ab_free[as]), aph ^ 1u)) {
                                 if (lane == 0) atomicExch(p.status, 32);
@@ -730,9 +729,6 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
                             ptx::tc_fence_after_sync();
                         }
                         if (warp == 0) TRACE(2, (int)si, 3 + 2 * h);
-#ifdef I4MM_NOST
-                        if (A[0] == 0x12345u && A[31] == 0x54321u)
-#endif
                         ptx::tmem_st32(lane_addr + C::kACol0 + as * 64 + h * 32, A);
                     }
                     if (!ok) break;
@@ -919,7 +915,6 @@ int umma_launch(int bits, bool sparse, const StreamParams& sp, int total_rows, i
     p.scales = sp.scales;
     p.zeros = sp.zeros;
     p.partials = sp.partials;
-    p.counters = sp.counters;
     p.status = sp.status;
     p.rows = total_rows;
     p.N = sp.N;
