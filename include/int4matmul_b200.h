@@ -51,10 +51,12 @@ int i4mm_last_cuda_error(void);
 int i4mm_version(void);
 
 /*
- * Bytes of device scratch the two multiply entries need.  The scratch holds per-CTA partial sums and
- * the arrival counters of the split-K reduction.  It must be zero-filled once before its first use;
- * the kernels leave the counters at zero again when they finish, so one buffer can serve every later
- * call on the same stream.  Calls that overlap on the device must not share a buffer.
+ * Bytes of device scratch the two multiply entries need.  The scratch holds the per-CTA partial tiles
+ * of the split-K reduction (tagged words on the tcgen05 path, plus arrival counters on the streaming
+ * path) and a status word.  It must be zero-filled once before its first use; the kernels leave it
+ * all-zero again when they finish, so one buffer can serve every later call on the same stream.
+ * Calls that overlap on the device must not share a buffer.  After a call for which
+ * i4mm_device_status reported I4MM_ERR_TIMEOUT, zero the buffer again before reusing it.
  */
 size_t i4mm_workspace_bytes(void);
 
@@ -70,7 +72,9 @@ size_t i4mm_workspace_bytes(void);
  *
  * rows = B*M may be any value >= 0 (rows == 0 returns I4MM_OK without a launch).  The entry picks the
  * weight-streaming kernel for few rows and the tcgen05 tensor-core kernel for many; `path` forces one:
- *   0 = automatic, 1 = streaming (mma.sync, split-K over the whole GPU), 2 = tcgen05 / TMEM pipeline.
+ *   0 = automatic (the tcgen05 kernel when the driver's tensor-map encoder is found), 1 = streaming (mma.sync,
+ *   split-K over the whole GPU), 2 = tcgen05 / TMEM pipeline (128 rows or more run as CTA pairs, two SMs per
+ *   MMA), 3 = tcgen05 with single CTAs only.
  */
 int i4mm_quant_matmul(int bits, int accumulate, int path,
                       void* out, const void* matrix, const void* mask /* NULL = dense */,

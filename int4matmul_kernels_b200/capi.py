@@ -16,7 +16,7 @@ OK = 0
 ERR_BITS, ERR_UNSUPPORTED, ERR_SHAPE, ERR_NULL, ERR_ALIGN = 1, 2, 3, 4, 5
 ERR_WORKSPACE, ERR_LAUNCH, ERR_MASK, ERR_DEVICE, ERR_TIMEOUT, ERR_TOO_LARGE = 6, 7, 8, 9, 10, 11
 
-PATH_AUTO, PATH_STREAM, PATH_TCGEN05 = 0, 1, 2
+PATH_AUTO, PATH_STREAM, PATH_TCGEN05, PATH_TCGEN05_SINGLE_CTA = 0, 1, 2, 3
 
 # every symbol the header declares, with its ctypes signature
 _SIGNATURES = {

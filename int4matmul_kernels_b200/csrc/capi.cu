@@ -11,7 +11,7 @@ cudaError_t sparse_pack_launch(void* wt_out, void* msk_out, const void* wt_in, c
 cudaError_t check_mask_launch(const void* mask, size_t count, void* violations, cudaStream_t stream);
 cudaError_t rownorm_launch(int mode, void* y, const void* a, const void* b, const void* c, long long rows, int width,
                            long long sa, long long sb, long long sc, cudaStream_t stream);
-int umma_launch(int bits, bool sparse, const StreamParams& p, int total_rows, int n_groups, int group_size,
+int umma_launch(int bits, bool sparse, const StreamParams& p, int total_rows, int n_groups, int group_size, int cta_pairs,
                 cudaStream_t stream, cudaError_t* cuda_err);
 bool umma_supported(int bits, bool sparse, int total_rows, int N, int S);
 }  // namespace i4mm
@@ -82,7 +82,7 @@ int i4mm_quant_matmul(int bits, int accumulate, int path,
     if (!aligned16(out) || !aligned16(matrix) || !aligned16(x) || !aligned16(scales) || !aligned16(zeros) ||
         (mask && !aligned16(mask)))
         return I4MM_ERR_ALIGN;
-    if (path < 0 || path > 2) return I4MM_ERR_SHAPE;
+    if (path < 0 || path > 3) return I4MM_ERR_SHAPE;
 
     i4mm::StreamParams p{};
     p.out = (__half*)out;
@@ -108,7 +108,7 @@ int i4mm_quant_matmul(int bits, int accumulate, int path,
 
     cudaStream_t st = (cudaStream_t)stream;
     bool use_umma = false;
-    if (path == 2) {
+    if (path >= 2) {
         if (!i4mm::umma_supported(bits, sparse, (int)rows, (int)N, (int)S)) return I4MM_ERR_UNSUPPORTED;
         use_umma = true;
     } else if (path == 0) {
@@ -116,7 +116,7 @@ int i4mm_quant_matmul(int bits, int accumulate, int path,
     }
     if (use_umma) {
         cudaError_t ce = cudaSuccess;
-        const int rc = i4mm::umma_launch(bits, sparse, p, (int)rows, (int)n_groups, (int)(group_size < 0 ? -1 : group_size), st, &ce);
+        const int rc = i4mm::umma_launch(bits, sparse, p, (int)rows, (int)n_groups, (int)(group_size < 0 ? -1 : group_size), path == 3 ? 1 : 0, st, &ce);
         if (rc == I4MM_ERR_LAUNCH) return fail_cuda(ce);
         return rc;
     }

@@ -21,7 +21,8 @@
 // Configurations (Cfg<NT>): NT <= 32 rows stream the weights once from HBM - one CTA per SM, 4 dequant warpgroups,
 // 16 weight stages, 6 A / activation stages, and the (tile, unit) space cut into equal ranges per CTA (split-K over
 // the whole GPU, partial tiles summed through scratch in a fixed order).  NT = 64: two CTAs per SM, whole tiles.
-// NT >= 128: one CTA per SM, whole tiles, epilogue stores transposed through shared memory.
+// NT >= 128: one CTA per SM, whole tiles, epilogue stores transposed through shared memory; by default launched as
+// clusters of two CTAs that run each MMA together (cta_group::2, M = 256 over two SMs), see PAIR below.
 // Every wait is bounded and reports through the status word instead of hanging.
 #include "../../include/int4matmul_b200.h"
 
@@ -243,15 +244,16 @@ struct Cfg {
     static constexpr bool kEpiHandoff = kStream;                      // the MMA warp waits for the accumulator and wakes the epilogue warps (named barrier)
     static constexpr bool kDeferArrive = kStream;                     // a dequant warp announces an A stage only before its next wait (hides the tcgen05.wait::st latency)
     static constexpr bool kSZProducer = kStream;                      // scales / zeros are issued by a thread of their own
-    static constexpr int kWarps = 4 * kWG + (kEpiWarps ? 4 : 0) + 3 + (kSZProducer ? 1 : 0);  // + weight producer, activation producer, MMA issuer
+    // many rows: two epilogue warpgroups, each draining half of the accumulator's columns, so that the next tile's
+    // MMAs wait half as long for the accumulator
+    static constexpr int kEpiGroups = NT >= 128 ? 2 : 1;
+    static constexpr int kWarps = 4 * kWG + (kEpiWarps ? 4 * kEpiGroups : 0) + 3 + (kSZProducer ? 1 : 0);  // + weight producer, activation producer, MMA issuer
     static constexpr int kThreads = kWarps * 32;
     static constexpr int kDCols = NT < 32 ? 32 : NT;                  // accumulator columns
     static constexpr int kACol0 = kDCols;                             // A stages follow: 64 columns (128 k) each
     static constexpr int kColsUsed = kDCols + 64 * kABStages;
     static constexpr int kTmemCols = kColsUsed <= 256 ? 256 : 512;
     static constexpr bool kSplit = NT <= 32;                          // split-K over CTAs with a scratch reduction
-    static constexpr int kBHalfBytes = NT * 128;                      // one 64-k activation sub-tile
-    static constexpr int kBStageBytes = 2 * kBHalfBytes;
     static constexpr int kMinBlocks = kStream ? 1 : NT <= 64 ? 2 : 1;
 };
 
@@ -275,14 +277,22 @@ struct TensorMaps {
     CUtensorMap z;
 };
 
-template <int BITS, bool SPARSE, int NT>
+// PAIR: launched as clusters of two CTAs (two SMs) that run every MMA together (cta_group::2, M = 256): the pair's
+// tile is 256 weight columns x NT rows, each CTA dequantises its own 128 columns and loads only half of the rows of
+// the activation tile, which halves the L2 -> shared-memory traffic that bounds the many-row shapes.
+template <int BITS, bool SPARSE, int NT, bool PAIR>
 __global__ void __launch_bounds__(Cfg<NT>::kThreads, Cfg<NT>::kMinBlocks)
 umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
     using F = UFormat<BITS, SPARSE>;
     using WS = WStage<F>;
     using C = Cfg<NT>;
+    static_assert(!PAIR || (NT >= 128 && !C::kSplit && !C::kEpiHandoff), "CTA pairs are for the whole-tile, many-row shapes");
+    constexpr int kBHalfBytes = (PAIR ? NT / 2 : NT) * 128;        // one 64-k activation sub-tile held by this CTA
+    constexpr int kBStageBytes = 2 * kBHalfBytes;
+    // single CTAs at NT = 256 have no shared memory left for a second transposition tile: the second epilogue group idles
+    constexpr int kEpiGroups = (C::kEpiGroups == 2 && (PAIR || NT < 256)) ? 2 : 1;
     constexpr int kEpiWarp0 = 4 * C::kWG;                           // first epilogue warp (a multiple of 4: lane quarter = warp % 4)
-    constexpr int kWProducer = kEpiWarp0 + (C::kEpiWarps ? 4 : 0), kBProducer = kWProducer + 1, kMma = kWProducer + 2;
+    constexpr int kWProducer = kEpiWarp0 + (C::kEpiWarps ? 4 * C::kEpiGroups : 0), kBProducer = kWProducer + 1, kMma = kWProducer + 2;
     constexpr int kSZWarp = kWProducer + 3;                         // only when Cfg::kSZProducer
     constexpr int kABStages = C::kABStages;
     extern __shared__ __align__(1024) unsigned char smem[];      // [B ring (1024-aligned tiles)][W ring]
@@ -298,10 +308,11 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
     long long trace_gt0, trace_c0 = clock64();
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(trace_gt0));
 #endif
+    const uint32_t rank = PAIR ? ptx::cluster_ctarank() : 0u;       // in the pair; rank 0 leads (issues the MMAs, owns the pair's barriers)
     const uint32_t smem0 = (ptx::smem_u32(smem) + 1023u) & ~1023u;
     const uint32_t b_ring = smem0;
-    const uint32_t w_ring = smem0 + kABStages * C::kBStageBytes;
-    const uint32_t epi_tile = w_ring + C::kWStages * WS::kBytes;     // 4 KB transposition tile of the epilogue warps (NT >= 128)
+    const uint32_t w_ring = smem0 + kABStages * kBStageBytes;
+    const uint32_t epi_tile = w_ring + C::kWStages * WS::kBytes;     // 4 KB transposition tile per epilogue warpgroup (NT >= 128)
 
     // ---- set-up, spread over warps so that nothing waits for one thread ----
     // The weight producer's warp initialises the weight ring's barriers itself and does not wait for the rest of the
@@ -317,24 +328,31 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
         }
         ptx::fence_mbar_init();
         __syncwarp();
-        ptx::named_bar_arrive(3, C::kThreads);
+        if (PAIR) ptx::cluster_sync_all();        // the other CTA arrives on this one's barriers: both must be set up first
+        else ptx::named_bar_arrive(3, C::kThreads);
     } else {
         if (warp == 0) {
             if (lane < kABStages) {
-                ptx::mbar_init(ptx::smem_u32(&bars.ab_full[lane]), 4 + 1);
+                // a pair's stage is full when the dequant warps of both CTAs and both activation halves have arrived
+                ptx::mbar_init(ptx::smem_u32(&bars.ab_full[lane]), PAIR ? 4 + 4 + 1 : 4 + 1);
                 ptx::mbar_init(ptx::smem_u32(&bars.ab_free[lane]), 1);
             }
             if (lane == 31) {
                 ptx::mbar_init(ptx::smem_u32(&bars.d_full), 1);
-                ptx::mbar_init(ptx::smem_u32(&bars.d_empty), 4);
+                ptx::mbar_init(ptx::smem_u32(&bars.d_empty), (PAIR ? 8 : 4) * kEpiGroups);
                 s_abort = 0;
             }
             ptx::fence_mbar_init();
         }
         if (SPARSE && warp == 1 && lane < 16) lut[lane] = sparse_lut_entry(lane);
         if (warp == kMma) {
-            ptx::tmem_alloc(ptx::smem_u32(&tmem_base_smem), C::kTmemCols);
-            ptx::tmem_relinquish();
+            if (PAIR) {
+                ptx::tmem_alloc_pair(ptx::smem_u32(&tmem_base_smem), C::kTmemCols);
+                ptx::tmem_relinquish_pair();
+            } else {
+                ptx::tmem_alloc(ptx::smem_u32(&tmem_base_smem), C::kTmemCols);
+                ptx::tmem_relinquish();
+            }
         }
         if (warp == kBProducer && lane == 0) {
             ptx::prefetch_tmap(&tm.x);
@@ -342,15 +360,20 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
             ptx::prefetch_tmap(&tm.z);
         }
         ptx::tc_fence_before_sync();
-        ptx::named_bar_sync(3, C::kThreads);
+        if (PAIR) ptx::cluster_sync_all();
+        else ptx::named_bar_sync(3, C::kThreads);
         ptx::tc_fence_after_sync();
     }
     const uint32_t tmem_base = tmem_base_smem;       // not valid in the weight producer's warp, which never uses it
 
     // ---- this CTA's share of the (tile, unit) space; one unit = 128 k.  Whole tiles unless the split-K variant ----
     const long long U = p.U;
-    const long long n_tiles = (long long)p.MTILES * p.CT;
-    const long long G = gridDim.x, b = blockIdx.x;
+    const int CTd = PAIR ? (p.CT + 1) / 2 : p.CT;                  // column tiles of a CTA, or column-tile pairs of a CTA pair
+    const long long n_tiles = (long long)p.MTILES * CTd;
+    const long long G = PAIR ? gridDim.x / 2 : gridDim.x, b = PAIR ? blockIdx.x / 2 : blockIdx.x;
+    // tile index -> this CTA's column tile (may lie past the last one in a pair: loads are zero-filled, stores masked) and row tile
+    auto tile_ct = [&](long long tile) -> int { return (int)(tile % CTd) * (PAIR ? 2 : 1) + (int)rank; };
+    auto tile_mt = [&](long long tile) -> int { return (int)(tile / CTd); };
     long long t_lo, t_hi;
     if (C::kSplit) {
         t_lo = range_lo(n_tiles * U, G, b);
@@ -371,7 +394,7 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
                 const long long tile = t / U;                      // one 64-bit division per segment, none per unit
                 const int u0 = (int)(t - tile * U);
                 const int u1 = (int)min(U, u0 + (t_hi - t));
-                const int ct = (int)(tile % p.CT);
+                const int ct = tile_ct(tile);
                 for (int u = u0; u < u1; ++u, ++si) {
                     TRACE(0, (int)si, 0);
                     if (!ptx::mbar_wait_relaxed(ptx::smem_u32(&bars.w_empty[ws]), wph ^ 1u, 1600)) { atomicExch(p.status, 11); ok = false; break; }
@@ -400,7 +423,7 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
                 const long long tile = t / U;
                 const int u0 = (int)(t - tile * U);
                 const int u1 = (int)min(U, u0 + (t_hi - t));
-                const int ct = (int)(tile % p.CT);
+                const int ct = tile_ct(tile);
                 for (int u = u0; u < u1; ++u) {
                     if (!ptx::mbar_wait_relaxed(ptx::smem_u32(&bars.w_empty[ws]), wph ^ 1u, 1600)) { atomicExch(p.status, 13); ok = false; break; }
                     const uint32_t st = w_ring + ws * WS::kBytes, full = ptx::smem_u32(&bars.w_full[ws]);
@@ -422,14 +445,23 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
                 const long long tile = t / U;
                 const int u0 = (int)(t - tile * U);
                 const int u1 = (int)min(U, u0 + (t_hi - t));
-                const int mt = (int)(tile / p.CT);
+                const int mt = tile_mt(tile);
                 for (int u = u0; u < u1; ++u) {
                     if (!(C::kStream ? ptx::mbar_wait_relaxed(ptx::smem_u32(&bars.ab_free[s]), ph ^ 1u, 400)
                                      : ptx::mbar_wait(ptx::smem_u32(&bars.ab_free[s]), ph ^ 1u))) { atomicExch(p.status, 12); ok = false; break; }
                     const uint32_t full = ptx::smem_u32(&bars.ab_full[s]);
-                    ptx::mbar_arrive_expect_tx(full, (uint32_t)C::kBStageBytes);
-                    ptx::tma_load_2d(b_ring + s * C::kBStageBytes, &tm.x, u * 128, mt * NT, full);
-                    ptx::tma_load_2d(b_ring + s * C::kBStageBytes + C::kBHalfBytes, &tm.x, u * 128 + 64, mt * NT, full);
+                    if (PAIR) {
+                        // both CTAs' halves are counted on the leader's barrier, which expects the bytes of both
+                        const uint32_t lfull = ptx::map_to_cta(full, 0);
+                        if (rank == 0) ptx::mbar_arrive_expect_tx(full, 2u * (uint32_t)kBStageBytes);
+                        const int r0 = mt * NT + (int)rank * (NT / 2);
+                        ptx::tma_load_2d_pair(b_ring + s * kBStageBytes, &tm.x, u * 128, r0, lfull);
+                        ptx::tma_load_2d_pair(b_ring + s * kBStageBytes + kBHalfBytes, &tm.x, u * 128 + 64, r0, lfull);
+                    } else {
+                        ptx::mbar_arrive_expect_tx(full, (uint32_t)kBStageBytes);
+                        ptx::tma_load_2d(b_ring + s * kBStageBytes, &tm.x, u * 128, mt * NT, full);
+                        ptx::tma_load_2d(b_ring + s * kBStageBytes + kBHalfBytes, &tm.x, u * 128 + 64, mt * NT, full);
+                    }
                     if (++s == kABStages) { s = 0; ph ^= 1u; }
                 }
                 t += u1 - u0;
@@ -438,9 +470,10 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
     } else if (warp == kMma) {
         // =========================== MMA issuer: the warp walks the loop, one elected lane issues ===========================
         {
-            const uint32_t idesc = ptx::idesc_f16_m128(NT);
+            const uint32_t idesc = PAIR ? ptx::idesc_f16_m256(NT) : ptx::idesc_f16_m128(NT);
             uint32_t si = 0, seg = 0;
             bool ok = true;
+            if (PAIR && rank != 0) t_lo = t_hi;              // the leader issues for both CTAs
             for (long long t = t_lo; t < t_hi && ok;) {
                 const long long tile = t / U;
                 const int u0 = (int)(t - tile * U);
@@ -463,23 +496,36 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
                     }
                     TRACE(1, (int)si, 1);
                     ptx::tc_fence_after_sync();
-                    const uint64_t bdesc = ptx::smem_desc_sw128(b_ring + s * C::kBStageBytes);
+                    const uint64_t bdesc = ptx::smem_desc_sw128(b_ring + s * kBStageBytes);
                     const uint32_t a0 = tmem_base + C::kACol0 + s * 64;
                     if (ptx::elect_one()) {
 #pragma unroll
                         for (int k = 0; k < 8; ++k) {
                             // K = 16 per instruction: +8 columns of A; B: +32 bytes (2 descriptor units) inside a 64-k sub-tile
-                            const uint64_t bd = bdesc + (uint64_t)((k >> 2) * (C::kBHalfBytes >> 4) + (k & 3) * 2);
-                            ptx::umma_f16_ts(tmem_base, a0 + k * 8, bd, idesc, (u > u0 || k > 0) ? 1u : 0u);
+                            const uint64_t bd = bdesc + (uint64_t)((k >> 2) * (kBHalfBytes >> 4) + (k & 3) * 2);
+                            if (PAIR) ptx::umma_f16_ts_pair(tmem_base, a0 + k * 8, bd, idesc, (u > u0 || k > 0) ? 1u : 0u);
+                            else ptx::umma_f16_ts(tmem_base, a0 + k * 8, bd, idesc, (u > u0 || k > 0) ? 1u : 0u);
                         }
-                        ptx::tc_commit(ptx::smem_u32(&bars.ab_free[s]));
+                        if (PAIR) {                                      // the stage comes free in both CTAs
+                            ptx::tc_commit_pair(ptx::map_to_cta(ptx::smem_u32(&bars.ab_free[s]), 0));
+                            ptx::tc_commit_pair(ptx::map_to_cta(ptx::smem_u32(&bars.ab_free[s]), 1));
+                        } else {
+                            ptx::tc_commit(ptx::smem_u32(&bars.ab_free[s]));
+                        }
                     }
                     __syncwarp();
                     TRACE(1, (int)si, 2);
                     if (++s == kABStages) { s = 0; ph ^= 1u; }
                 }
                 if (!ok) break;
-                if (ptx::elect_one()) ptx::tc_commit(ptx::smem_u32(&bars.d_full));
+                if (ptx::elect_one()) {
+                    if (PAIR) {
+                        ptx::tc_commit_pair(ptx::map_to_cta(ptx::smem_u32(&bars.d_full), 0));
+                        ptx::tc_commit_pair(ptx::map_to_cta(ptx::smem_u32(&bars.d_full), 1));
+                    } else {
+                        ptx::tc_commit(ptx::smem_u32(&bars.d_full));
+                    }
+                }
                 __syncwarp();
                 TRACE(3, (int)seg, 6);
                 if (C::kEpiHandoff) {
@@ -506,7 +552,7 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
         // Accumulator of one finished segment -> fp16 rows of `out`, or a partial tile for the split-K reduction.
         // Run by 4 warps whose index modulo 4 selects the 32 tensor-memory lanes (= weight columns) they may read.
         auto epilogue = [&](uint32_t seg, long long tile, int u0, int u1, bool first_segment) -> bool {
-            const int mt = (int)(tile / p.CT), ct = (int)(tile - (long long)mt * p.CT);
+            const int mt = tile_mt(tile), ct = tile_ct(tile);
             const int col = (warp & 3) * 32 + lane;
             const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
             if (warp == kEpiWarp0 || (!C::kEpiWarps && warp == 0)) TRACE(3, (int)seg, 0);
@@ -543,22 +589,29 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
             if (C::kEpiTransposed) {
                 // 16 accumulator columns (= 16 output rows) at a time: transposed through a 4 KB shared-memory tile so that
                 // the global stores are 16-byte rows instead of one 2-byte element per lane
-                const uint32_t stage_tile = epi_tile;                       // [16 rows][128 columns] fp16
+                const int eg = (warp - kEpiWarp0) >> 2;                     // epilogue warpgroup: its share of the accumulator columns
+                const uint32_t stage_tile = epi_tile + eg * 4096;          // [16 rows][128 columns] fp16
+                const uint32_t bar_id = 1 + 3 * eg;                         // named barriers 1 and 4
                 const int t128 = (warp & 3) * 32 + lane;
+                constexpr int kShare = NT / kEpiGroups;
+                const int j_end = (eg + 1) * kShare;
 #pragma unroll 1
-                for (int j0 = 0; j0 < NT; j0 += 16) {
+                for (int j0 = eg * kShare; j0 < j_end; j0 += 16) {
                     uint32_t v[16];
                     ptx::tmem_ld16(lane_addr + j0, v);
                     ptx::tc_wait_ld();
-                    if (j0 + 16 >= NT) {                   // the last columns are in registers: the accumulator is free again
+                    if (j0 + 16 >= j_end) {                // this group's last columns are in registers: its share of the accumulator is free
                         ptx::tc_fence_before_sync();
                         __syncwarp();
-                        if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&bars.d_empty));
+                        if (lane == 0) {
+                            if (PAIR) ptx::mbar_arrive_cluster(ptx::map_to_cta(ptx::smem_u32(&bars.d_empty), 0));
+                            else ptx::mbar_arrive(ptx::smem_u32(&bars.d_empty));
+                        }
                     }
 #pragma unroll
                     for (int j = 0; j < 16; ++j)
                         ptx::sts16(stage_tile + j * 256 + col * 2, __half_as_ushort(__float2half_rn(__uint_as_float(v[j]))));
-                    ptx::named_bar_sync(1, 128);
+                    ptx::named_bar_sync(bar_id, 128);
 #pragma unroll
                     for (int r = 0; r < 2; ++r) {
                         const int idx = t128 + r * 128;                     // 256 chunks of 16 bytes: row = idx / 16, chunk = idx % 16
@@ -568,7 +621,7 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
                             *reinterpret_cast<uint4*>(p.out + (size_t)(row0 + m) * p.S + ct * 128 + c8) = q;
                         }
                     }
-                    ptx::named_bar_sync(1, 128);
+                    ptx::named_bar_sync(bar_id, 128);
                 }
             } else {
             constexpr int CH = NT >= 64 ? 32 : 16;          // accumulator columns per tensor-memory load
@@ -637,7 +690,9 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
             return true;
         };
 
-        if (C::kEpiWarps && warp >= kEpiWarp0) {
+        if (C::kEpiWarps && warp >= kEpiWarp0 + 4 * kEpiGroups) {
+            // (an epilogue warpgroup that this configuration does not use)
+        } else if (C::kEpiWarps && warp >= kEpiWarp0) {
             // ----- dedicated epilogue warps: one pass per segment -----
             uint32_t seg = 0;
             bool first_segment = true;
@@ -662,7 +717,10 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
                 ptx::tc_wait_st();
                 ptx::tc_fence_before_sync();
                 __syncwarp();
-                if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&bars.ab_full[stage]));
+                if (lane == 0) {
+                    if (PAIR) ptx::mbar_arrive_cluster(ptx::map_to_cta(ptx::smem_u32(&bars.ab_full[stage]), 0));
+                    else ptx::mbar_arrive(ptx::smem_u32(&bars.ab_full[stage]));
+                }
             };
             bool ok = true;
             bool first_segment = true;
@@ -751,7 +809,11 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
     ptx::tc_fence_before_sync();
     __syncthreads();
     ptx::tc_fence_after_sync();
-    if (warp == kMma) ptx::tmem_dealloc(tmem_base, C::kTmemCols);
+    if (PAIR) ptx::cluster_sync_all();       // neither CTA's barriers or tensor memory may go while the other can still reach them
+    if (warp == kMma) {
+        if (PAIR) ptx::tmem_dealloc_pair(tmem_base, C::kTmemCols);
+        else ptx::tmem_dealloc(tmem_base, C::kTmemCols);
+    }
 #ifdef I4MM_TRACE
     if (threadIdx.x == 0 && blockIdx.x < 1024) {
         long long gt1;
@@ -800,13 +862,14 @@ bool encode_2d(CUtensorMap* out, const void* base, CUtensorMapDataType dt, int e
                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int BITS, bool SPARSE, int NT>
+template <int BITS, bool SPARSE, int NT, bool PAIR>
 int launch_nt(const UmmaParams& p, const __half* x, int n_groups, cudaStream_t stream, cudaError_t* cuda_err) {
     using F = UFormat<BITS, SPARSE>;
     using C = Cfg<NT>;
+    constexpr int kBStageBytes = 2 * (PAIR ? NT / 2 : NT) * 128;
     TensorMaps tm;
     const uint64_t R = SPARSE ? (uint64_t)p.N / 16 : (uint64_t)p.N * BITS / 32;
-    bool ok = encode_2d(&tm.x, x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, p.rows, p.N, NT, 64, CU_TENSOR_MAP_SWIZZLE_128B);
+    bool ok = encode_2d(&tm.x, x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, p.rows, p.N, PAIR ? NT / 2 : NT, 64, CU_TENSOR_MAP_SWIZZLE_128B);
     ok = ok && encode_2d(&tm.w, p.matrix, CU_TENSOR_MAP_DATA_TYPE_INT32, 4, R, p.S, 2 * F::WROWS, 128, CU_TENSOR_MAP_SWIZZLE_NONE);
     if (SPARSE)
         ok = ok && encode_2d(&tm.m, p.mask, CU_TENSOR_MAP_DATA_TYPE_INT32, 4, (uint64_t)p.N / 32, p.S, 2 * F::MROWS, 128,
@@ -817,9 +880,9 @@ int launch_nt(const UmmaParams& p, const __half* x, int n_groups, cudaStream_t s
     ok = ok && encode_2d(&tm.z, p.zeros, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, n_groups, p.S, 2, 128, CU_TENSOR_MAP_SWIZZLE_NONE);
     if (!ok) return I4MM_ERR_DEVICE;
 
-    const size_t smem = 1024 + (size_t)C::kABStages * C::kBStageBytes + (size_t)C::kWStages * WStage<F>::kBytes +
-                        (C::kEpiTransposed ? 4096 : 0);
-    auto kern = umma_kernel<BITS, SPARSE, NT>;
+    const size_t smem = 1024 + (size_t)C::kABStages * kBStageBytes + (size_t)C::kWStages * WStage<F>::kBytes +
+                        (C::kEpiTransposed ? 4096 * ((C::kEpiGroups == 2 && (PAIR || NT < 256)) ? 2 : 1) : 0);
+    auto kern = umma_kernel<BITS, SPARSE, NT, PAIR>;
     static int ctas_per_sm[16] = {0};
     static int sm_count[16] = {0};
     int dev = 0;
@@ -842,11 +905,43 @@ int launch_nt(const UmmaParams& p, const __half* x, int n_groups, cudaStream_t s
         sm_count[dev] = sms;
         ctas_per_sm[dev] = n > 0 ? n : 1;
     }
+    if (PAIR) {
+        // clusters of two CTAs; as many as can be resident at once, each walking its share of the pair tiles
+        static int max_clusters[16] = {0};
+        cudaLaunchConfig_t cfg = {};
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.blockDim = dim3(C::kThreads, 1, 1);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = stream;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        if (max_clusters[dev] == 0) {
+            cfg.gridDim = dim3(2 * (sm_count[dev] / 2), 1, 1);
+            int n = 0;
+            if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0) {
+                (void)cudaGetLastError();
+                n = sm_count[dev] / 2;
+            }
+            if (n > sm_count[dev] / 2) n = sm_count[dev] / 2;
+            max_clusters[dev] = n;
+        }
+        long long clusters = max_clusters[dev];
+        const long long work = (long long)p.MTILES * ((p.CT + 1) / 2);
+        if (clusters > work) clusters = work;
+        cfg.gridDim = dim3((unsigned)(2 * clusters), 1, 1);
+        e = cudaLaunchKernelEx(&cfg, kern, tm, p);
+        if (e != cudaSuccess) { *cuda_err = e; return I4MM_ERR_LAUNCH; }
+        return I4MM_OK;
+    }
     const long long n_tiles = (long long)p.MTILES * p.CT;
     long long grid = (long long)sm_count[dev] * ctas_per_sm[dev];
     const long long work = C::kSplit ? n_tiles * p.U : n_tiles;
     if (grid > work) grid = work;
-    if (C::kSplit && grid > 148 * 4) grid = 148 * 4;        // the scratch holds two partial tiles per CTA for this many CTAs
+    if (C::kSplit && grid > 148 * 4) grid = 148 * 4;        // the scratch holds one partial tile per CTA for this many CTAs
     kern<<<(int)grid, C::kThreads, smem, stream>>>(tm, p);
     e = cudaGetLastError();
     if (e != cudaSuccess) { *cuda_err = e; return I4MM_ERR_LAUNCH; }
@@ -874,8 +969,10 @@ int choose_tile_rows(int rows, int col_tiles, int sms) {
     return best;
 }
 
+constexpr int kPairMinRows = 128;
+
 template <int BITS, bool SPARSE>
-int launch_fmt(UmmaParams& p, const __half* x, int n_groups, cudaStream_t stream, cudaError_t* cuda_err) {
+int launch_fmt(UmmaParams& p, const __half* x, int n_groups, int pair_mode, cudaStream_t stream, cudaError_t* cuda_err) {
     static int sms = 0;
     if (sms == 0) {
         int dev = 0, n = 0;
@@ -884,17 +981,29 @@ int launch_fmt(UmmaParams& p, const __half* x, int n_groups, cudaStream_t stream
         else
             sms = 148;
     }
-    const int nt = choose_tile_rows(p.rows, p.CT, sms);
+    // 128 rows or more (the whole-tile configurations) run as CTA pairs, two SMs per MMA, unless the caller asked for single CTAs
+    const bool pair = pair_mode == 0 && p.rows >= kPairMinRows;
+    const int nt = pair ? choose_tile_rows(p.rows, (p.CT + 1) / 2, sms / 2) : choose_tile_rows(p.rows, p.CT, sms);
     p.MTILES = (p.rows + nt - 1) / nt;
+    if (pair) {
+        switch (nt) {
+            case 128: return launch_nt<BITS, SPARSE, 128, true>(p, x, n_groups, stream, cuda_err);
+            case 160: return launch_nt<BITS, SPARSE, 160, true>(p, x, n_groups, stream, cuda_err);
+            case 192: return launch_nt<BITS, SPARSE, 192, true>(p, x, n_groups, stream, cuda_err);
+            case 224: return launch_nt<BITS, SPARSE, 224, true>(p, x, n_groups, stream, cuda_err);
+            case 256: return launch_nt<BITS, SPARSE, 256, true>(p, x, n_groups, stream, cuda_err);
+            default: break;
+        }
+    }
     switch (nt) {
-        case 16: return launch_nt<BITS, SPARSE, 16>(p, x, n_groups, stream, cuda_err);
-        case 32: return launch_nt<BITS, SPARSE, 32>(p, x, n_groups, stream, cuda_err);
-        case 64: return launch_nt<BITS, SPARSE, 64>(p, x, n_groups, stream, cuda_err);
-        case 128: return launch_nt<BITS, SPARSE, 128>(p, x, n_groups, stream, cuda_err);
-        case 160: return launch_nt<BITS, SPARSE, 160>(p, x, n_groups, stream, cuda_err);
-        case 192: return launch_nt<BITS, SPARSE, 192>(p, x, n_groups, stream, cuda_err);
-        case 224: return launch_nt<BITS, SPARSE, 224>(p, x, n_groups, stream, cuda_err);
-        default: return launch_nt<BITS, SPARSE, 256>(p, x, n_groups, stream, cuda_err);
+        case 16: return launch_nt<BITS, SPARSE, 16, false>(p, x, n_groups, stream, cuda_err);
+        case 32: return launch_nt<BITS, SPARSE, 32, false>(p, x, n_groups, stream, cuda_err);
+        case 64: return launch_nt<BITS, SPARSE, 64, false>(p, x, n_groups, stream, cuda_err);
+        case 128: return launch_nt<BITS, SPARSE, 128, false>(p, x, n_groups, stream, cuda_err);
+        case 160: return launch_nt<BITS, SPARSE, 160, false>(p, x, n_groups, stream, cuda_err);
+        case 192: return launch_nt<BITS, SPARSE, 192, false>(p, x, n_groups, stream, cuda_err);
+        case 224: return launch_nt<BITS, SPARSE, 224, false>(p, x, n_groups, stream, cuda_err);
+        default: return launch_nt<BITS, SPARSE, 256, false>(p, x, n_groups, stream, cuda_err);
     }
 }
 
@@ -905,7 +1014,7 @@ bool umma_supported(int bits, bool sparse, int total_rows, int N, int S) {
     return total_rows >= 1 && N >= 64 && encode_tiled_fn() != nullptr;
 }
 
-int umma_launch(int bits, bool sparse, const StreamParams& sp, int total_rows, int n_groups, int group_size,
+int umma_launch(int bits, bool sparse, const StreamParams& sp, int total_rows, int n_groups, int group_size, int cta_pairs /* 0 by shape, 1 never */,
                 cudaStream_t stream, cudaError_t* cuda_err) {
     (void)group_size;
     UmmaParams p{};
@@ -923,10 +1032,10 @@ int umma_launch(int bits, bool sparse, const StreamParams& sp, int total_rows, i
     p.CT = sp.CT;
     p.accumulate = sp.accumulate;
     p.gdiv = sp.gdiv;
-    if (sparse) return launch_fmt<4, true>(p, sp.x, n_groups, stream, cuda_err);
-    if (bits == 4) return launch_fmt<4, false>(p, sp.x, n_groups, stream, cuda_err);
-    if (bits == 3) return launch_fmt<3, false>(p, sp.x, n_groups, stream, cuda_err);
-    return launch_fmt<2, false>(p, sp.x, n_groups, stream, cuda_err);
+    if (sparse) return launch_fmt<4, true>(p, sp.x, n_groups, cta_pairs, stream, cuda_err);
+    if (bits == 4) return launch_fmt<4, false>(p, sp.x, n_groups, cta_pairs, stream, cuda_err);
+    if (bits == 3) return launch_fmt<3, false>(p, sp.x, n_groups, cta_pairs, stream, cuda_err);
+    return launch_fmt<2, false>(p, sp.x, n_groups, cta_pairs, stream, cuda_err);
 }
 
 }  // namespace i4mm

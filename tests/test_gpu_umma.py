@@ -96,6 +96,28 @@ def test_matmul_shapes_like_the_benchmark(shape):
     assert st["frac_exact"] > 0.8
 
 
+@pytest.mark.parametrize("fmt", FORMATS, ids=fmt_id)
+@pytest.mark.parametrize("m", [128, 129, 300, 700])
+def test_single_cta_path_matches_cta_pairs_bit_for_bit(fmt, m):
+    """128 rows or more run as CTA pairs (two SMs per MMA) by default; path 3 keeps single CTAs.  Same k order per
+    output element, so the two must agree exactly, and both with the oracle."""
+    bits, sparse = fmt
+    p = oracle.make_problem(bits, 640, 384, m, 128, sparse=sparse, seed=300 + m)
+    pair = run_problem(p, path=P)
+    single = run_problem(p, path=capi.PATH_TCGEN05_SINGLE_CTA)
+    want, _, bound = oracle.expected(p)
+    assert_parity(single, want, bound, f"single-CTA rows={m} {fmt}")
+    assert np.array_equal(pair.view(np.uint16), single.view(np.uint16))
+
+
+@pytest.mark.parametrize("s", [128, 256, 640, 1152])
+def test_cta_pairs_with_odd_and_even_column_tile_counts(s):
+    p = oracle.make_problem(4, 1024, s, 520, 128, seed=s)
+    got = run_problem(p, path=P)
+    want, _, bound = oracle.expected(p)
+    assert_parity(got, want, bound, f"pairs S={s}")
+
+
 def test_no_device_timeouts_recorded():
     ws = ops.workspace(torch.device("cuda", torch.cuda.current_device()), torch.cuda.current_stream())
     assert capi.load().i4mm_device_status(ws.data_ptr(), torch.cuda.current_stream().cuda_stream) == capi.OK
