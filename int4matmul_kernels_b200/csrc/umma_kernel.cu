@@ -257,6 +257,13 @@ struct Cfg {
     static constexpr int kMinBlocks = kStream ? 1 : NT <= 64 ? 2 : 1;
 };
 
+// A / activation stages.  A CTA of a pair holds only half of each activation tile, which leaves shared memory for as
+// many stages as tensor memory has columns for (accumulator + 64 per stage <= 512).
+template <int NT, bool PAIR>
+struct ABStages {
+    static constexpr int value = !PAIR ? Cfg<NT>::kABStages : (Cfg<NT>::kDCols + 64 * 5 <= 512 ? 5 : 4);
+};
+
 struct Barriers {
     unsigned long long w_full[kMaxWStages], w_empty[kMaxWStages];
     unsigned long long ab_full[kMaxABStages];  // 4 dequant warps + the activation producer (with its transaction bytes)
@@ -294,7 +301,7 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
     constexpr int kEpiWarp0 = 4 * C::kWG;                           // first epilogue warp (a multiple of 4: lane quarter = warp % 4)
     constexpr int kWProducer = kEpiWarp0 + (C::kEpiWarps ? 4 * C::kEpiGroups : 0), kBProducer = kWProducer + 1, kMma = kWProducer + 2;
     constexpr int kSZWarp = kWProducer + 3;                         // only when Cfg::kSZProducer
-    constexpr int kABStages = C::kABStages;
+    constexpr int kABStages = ABStages<NT, PAIR>::value;
     extern __shared__ __align__(1024) unsigned char smem[];      // [B ring (1024-aligned tiles)][W ring]
     __shared__ __align__(8) Barriers bars;
     __shared__ uint4 lut[16];
@@ -880,7 +887,7 @@ int launch_nt(const UmmaParams& p, const __half* x, int n_groups, cudaStream_t s
     ok = ok && encode_2d(&tm.z, p.zeros, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, n_groups, p.S, 2, 128, CU_TENSOR_MAP_SWIZZLE_NONE);
     if (!ok) return I4MM_ERR_DEVICE;
 
-    const size_t smem = 1024 + (size_t)C::kABStages * kBStageBytes + (size_t)C::kWStages * WStage<F>::kBytes +
+    const size_t smem = 1024 + (size_t)ABStages<NT, PAIR>::value * kBStageBytes + (size_t)C::kWStages * WStage<F>::kBytes +
                         (C::kEpiTransposed ? 4096 * ((C::kEpiGroups == 2 && (PAIR || NT < 256)) ? 2 : 1) : 0);
     auto kern = umma_kernel<BITS, SPARSE, NT, PAIR>;
     static int ctas_per_sm[16] = {0};
