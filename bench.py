@@ -57,8 +57,8 @@ DEFAULT_WORKLOAD = "int4_matmul_m2048_5120x20480"
 # DRAM bytes per launch of the dominant kernel from ncu captures (dram__bytes_read.sum + dram__bytes_write.sum);
 # the summaries are under profiles/.  None = not captured for that workload.
 NCU_TRAFFIC_BYTES = {
-    "int4_matmul_m2048_5120x20480": 193.5e6,    # profiles/umma_kernel_int4_matmul_m2048_5120x20480.md
-    "int4_matvec_16384": 143.2e6,               # profiles/umma_kernel_int4_matvec_16384.md
+    "int4_matmul_m2048_5120x20480": 298.9e6,    # profiles/umma_kernel_int4_matmul_m2048_5120x20480.md
+    "int4_matvec_16384": 146.4e6,               # profiles/umma_kernel_int4_matvec_16384.md
 }
 
 L2_BYTES = 126 * 1024 * 1024
