@@ -799,7 +799,8 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
                         ptx::tmem_st32(lane_addr + C::kACol0 + as * 64 + h * 32, A);
                     }
                     if (!ok) break;
-                    if (C::kDeferArrive) pending = (int)as;
+                    // (not deferred for the warpgroup's first stage: the pipeline is still filling and the MMA warp is waiting)
+                    if (C::kDeferArrive && si >= (uint32_t)C::kWG) pending = (int)as;
                     else announce((int)as);
                     if (warp == 0) TRACE(2, (int)si, 6);
                 }
