@@ -522,7 +522,8 @@ def main():
         achieved = algorithmic_flops(w, s_local) / 1e12 / (ms_step / 1e3)
         peak, runit = peaks["tf_burst"], "TFLOP/s"
     roofline = dict(bound=kind, achieved=achieved, peak=peak, unit=runit, frac=achieved / peak,
-                    traffic=NCU_TRAFFIC_BYTES.get(args.workload), peak_source=peaks["source"],
+                    traffic=NCU_TRAFFIC_BYTES.get(args.workload) if world == 1 else None,   # captured for the unsharded launch only
+                    peak_source=peaks["source"],
                     us_per_launch=us_launch, kernel="umma_kernel (tcgen05)" if use_umma else "stream_kernel (mma.sync)",
                     frac_of_nominal=achieved / (8000.0 if kind == "hbm" else 2250.0))
 
