@@ -604,6 +604,37 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
                 const int t128 = (warp & 3) * 32 + lane;
                 constexpr int kShare = NT / kEpiGroups;
                 const int j_end = (eg + 1) * kShare;
+                if (PAIR) {
+                    // A CTA of a pair has the shared memory to stage its whole share as fp16 ([kShare rows][128 columns]):
+                    // the accumulator is released after the tensor-memory loads and conversions alone, and the global
+                    // stores run while the next tile's MMAs are already under way.
+                    const uint32_t stage = epi_tile + eg * (kShare * 256);
+#pragma unroll 1
+                    for (int j0 = eg * kShare; j0 < j_end; j0 += 16) {
+                        uint32_t v[16];
+                        ptx::tmem_ld16(lane_addr + j0, v);
+                        ptx::tc_wait_ld();
+                        if (j0 + 16 >= j_end) {
+                            ptx::tc_fence_before_sync();
+                            __syncwarp();
+                            if (lane == 0) ptx::mbar_arrive_cluster(ptx::map_to_cta(ptx::smem_u32(&bars.d_empty), 0));
+                        }
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            ptx::sts16(stage + (j0 - eg * kShare + j) * 256 + col * 2,
+                                       __half_as_ushort(__float2half_rn(__uint_as_float(v[j]))));
+                    }
+                    ptx::named_bar_sync(bar_id, 128);
+#pragma unroll 1
+                    for (int idx = t128; idx < kShare * 16; idx += 128) {   // 16-byte chunks: row = idx / 16, chunk = idx % 16
+                        const int m = eg * kShare + (idx >> 4), c8 = (idx & 15) * 8;
+                        if (m < nrows && ct * 128 + c8 < p.S) {
+                            const uint4 q = ptx::lds128(stage + (idx >> 4) * 256 + c8 * 2);
+                            *reinterpret_cast<uint4*>(p.out + (size_t)(row0 + m) * p.S + ct * 128 + c8) = q;
+                        }
+                    }
+                    ptx::named_bar_sync(bar_id, 128);                       // the staging area may be written again
+                } else
 #pragma unroll 1
                 for (int j0 = eg * kShare; j0 < j_end; j0 += 16) {
                     uint32_t v[16];
@@ -891,7 +922,7 @@ int launch_nt(const UmmaParams& p, const __half* x, int n_groups, cudaStream_t s
     if (!ok) return I4MM_ERR_DEVICE;
 
     const size_t smem = 1024 + (size_t)ABStages<NT, PAIR>::value * kBStageBytes + (size_t)C::kWStages * WStage<F>::kBytes +
-                        (C::kEpiTransposed ? 4096 * ((C::kEpiGroups == 2 && (PAIR || NT < 256)) ? 2 : 1) : 0);
+                        (!C::kEpiTransposed ? 0 : PAIR ? NT * 256 : 4096 * ((C::kEpiGroups == 2 && NT < 256) ? 2 : 1));
     auto kern = umma_kernel<BITS, SPARSE, NT, PAIR>;
     static int ctas_per_sm[16] = {0};
     static int sm_count[16] = {0};
