@@ -236,9 +236,12 @@ struct Cfg {
     // packed-weight ring (128 k per stage).  Few rows: the kernel streams weights from HBM, and the ring has to
     // cover the DRAM latency; many rows: weights are a trickle next to the activation tiles
     static constexpr bool kStream = NT <= 32;                         // weight-streaming shapes: one CTA per SM with everything doubled
-    static constexpr int kWStages = kStream ? 16 : NT <= 64 ? 8 : 3;
-    static constexpr int kWG = kStream ? 4 : 2;                       // dequant warpgroups (4 warps each), taking units in turn
-    static constexpr int kABStages = kStream ? 6 : 3;                 // ring of (A in tensor memory, activation tile in shared memory) pairs, 128 k per stage
+    // NT = 128 (65..128 rows): an MMA of N = 128 takes half as long as the dequantisation of its weights with two
+    // warpgroups, so this shape gets four as well, and a deeper ring
+    static constexpr bool kDequantBound = NT == 128;
+    static constexpr int kWStages = kStream ? 16 : NT <= 64 ? 8 : kDequantBound ? 6 : 3;
+    static constexpr int kWG = (kStream || kDequantBound) ? 4 : 2;    // dequant warpgroups (4 warps each), taking units in turn
+    static constexpr int kABStages = kStream ? 6 : kDequantBound ? 4 : 3;   // ring of (A in tensor memory, activation tile in shared memory) pairs, 128 k per stage
     static constexpr bool kEpiWarps = NT >= 128 || kStream;           // a warpgroup of its own for the epilogue (else dequant warpgroup 0 does it)
     static constexpr bool kEpiTransposed = NT >= 128;                 // epilogue stores go through a shared-memory transposition tile
     static constexpr bool kEpiHandoff = kStream;                      // the MMA warp waits for the accumulator and wakes the epilogue warps (named barrier)
@@ -253,7 +256,11 @@ struct Cfg {
     static constexpr int kACol0 = kDCols;                             // A stages follow: 64 columns (128 k) each
     static constexpr int kColsUsed = kDCols + 64 * kABStages;
     static constexpr int kTmemCols = kColsUsed <= 256 ? 256 : 512;
-    static constexpr bool kSplit = NT <= 32;                          // split-K over CTAs with a scratch reduction
+    // split-K over CTAs with a scratch reduction.  The code handles tiles of up to 128 rows, but the reducing CTA reads
+    // its partners' partial tiles in dependent L2 round trips (rows x partners / 8 of them): measured at 128 rows that
+    // costs 15-30 K cycles per tile and loses more than the better balance gains, so only the few-row shapes split.
+    static constexpr bool kSplit = NT <= 32;
+    static constexpr int kSlotElems = kDCols * 128;                   // 64-bit words of one CTA's partial tile in the scratch
     static constexpr int kMinBlocks = kStream ? 1 : NT <= 64 ? 2 : 1;
 };
 
@@ -293,7 +300,7 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
     using F = UFormat<BITS, SPARSE>;
     using WS = WStage<F>;
     using C = Cfg<NT>;
-    static_assert(!PAIR || (NT >= 128 && !C::kSplit && !C::kEpiHandoff), "CTA pairs are for the whole-tile, many-row shapes");
+    static_assert(!PAIR || (NT >= 128 && !C::kEpiHandoff), "CTA pairs are for the many-row shapes");
     constexpr int kBHalfBytes = (PAIR ? NT / 2 : NT) * 128;        // one 64-k activation sub-tile held by this CTA
     constexpr int kBStageBytes = 2 * kBHalfBytes;
     // single CTAs at NT = 256 have no shared memory left for a second transposition tile: the second epilogue group idles
@@ -592,9 +599,48 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
                 const long long T = n_tiles * U, lo_t = tile * U;
                 b_lo = range_owner(T, G, lo_t);
                 b_hi = range_owner(T, G, lo_t + U - 1);
-                if ((int)b != b_lo) slot = partials64 + (size_t)b * (32 * 128);
+                if ((int)b != b_lo) slot = partials64 + (size_t)(PAIR ? b * 2 + rank : b) * C::kSlotElems;
             }
             (void)first_segment;
+            // leaves accumulator rows j0 .. j0 + n - 1 of this lane's column in this CTA's slot
+            auto put_partial = [&](auto& v, int j0) {
+                constexpr int CNT = (int)(sizeof(v) / sizeof(uint32_t));
+#pragma unroll
+                for (int j = 0; j < CNT; ++j)
+                    if (j0 + j < nrows) ptx::st_relaxed_gpu_u64(slot + (j0 + j) * 128 + col, (1ull << 32) | v[j]);
+            };
+            // adds the other CTAs' partial rows j0 .. j0 + n - 1 to v, in CTA order, and clears them
+            auto add_partials = [&](auto& v, int j0) {
+                constexpr int CNT = (int)(sizeof(v) / sizeof(uint32_t));
+                bool waiting_ok = true;
+                for (int bb = b_lo + 1; bb <= b_hi; ++bb) {
+                    unsigned long long* src = partials64 + (size_t)(PAIR ? bb * 2 + (int)rank : bb) * C::kSlotElems + col;
+#pragma unroll
+                    for (int jb = 0; jb < CNT; jb += 8) {
+                        if (j0 + jb >= nrows) break;                       // warp-uniform
+                        unsigned long long w[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i)
+                            if (j0 + jb + i < nrows) w[i] = ptx::ld_relaxed_gpu_u64(src + (j0 + jb + i) * 128);
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            if (j0 + jb + i < nrows) {
+                                for (uint32_t spins = 0; (uint32_t)(w[i] >> 32) != 1u && waiting_ok; ++spins) {
+                                    if (spins >= ptx::kSpinLimit) {        // a contributor never delivered: report, stop waiting
+                                        atomicExch(p.status, 34);
+                                        waiting_ok = false;
+                                        break;
+                                    }
+                                    __nanosleep(64);
+                                    w[i] = ptx::ld_relaxed_gpu_u64(src + (j0 + jb + i) * 128);
+                                }
+                                v[jb + i] = __float_as_uint(__uint_as_float(v[jb + i]) + __uint_as_float((uint32_t)w[i]));
+                                ptx::st_relaxed_gpu_u64(src + (j0 + jb + i) * 128, 0ull);
+                            }
+                        }
+                    }
+                }
+            };
             if (C::kEpiTransposed) {
                 // 16 accumulator columns (= 16 output rows) at a time: transposed through a 4 KB shared-memory tile so that
                 // the global stores are 16-byte rows instead of one 2-byte element per lane
@@ -619,6 +665,13 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
                             __syncwarp();
                             if (lane == 0) ptx::mbar_arrive_cluster(ptx::map_to_cta(ptx::smem_u32(&bars.d_empty), 0));
                         }
+                        if (C::kSplit) {
+                            if (slot) {
+                                put_partial(v, j0);
+                                continue;
+                            }
+                            if (b_hi > b_lo) add_partials(v, j0);
+                        }
 #pragma unroll
                         for (int j = 0; j < 16; ++j)
                             ptx::sts16(stage + (j0 - eg * kShare + j) * 256 + col * 2,
@@ -626,7 +679,7 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
                     }
                     ptx::named_bar_sync(bar_id, 128);
 #pragma unroll 1
-                    for (int idx = t128; idx < kShare * 16; idx += 128) {   // 16-byte chunks: row = idx / 16, chunk = idx % 16
+                    for (int idx = t128; idx < (slot ? 0 : kShare * 16); idx += 128) {   // 16-byte chunks: row = idx / 16, chunk = idx % 16
                         const int m = eg * kShare + (idx >> 4), c8 = (idx & 15) * 8;
                         if (m < nrows && ct * 128 + c8 < p.S) {
                             const uint4 q = ptx::lds128(stage + (idx >> 4) * 256 + c8 * 2);
@@ -647,6 +700,13 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
                             if (PAIR) ptx::mbar_arrive_cluster(ptx::map_to_cta(ptx::smem_u32(&bars.d_empty), 0));
                             else ptx::mbar_arrive(ptx::smem_u32(&bars.d_empty));
                         }
+                    }
+                    if (C::kSplit) {
+                        if (slot) {
+                            put_partial(v, j0);
+                            continue;
+                        }
+                        if (b_hi > b_lo) add_partials(v, j0);
                     }
 #pragma unroll
                     for (int j = 0; j < 16; ++j)
@@ -677,41 +737,10 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
                     if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&bars.d_empty));
                 }
                 if (slot) {
-#pragma unroll
-                    for (int j = 0; j < CH; ++j)
-                        if (j0 + j < nrows) ptx::st_relaxed_gpu_u64(slot + (j0 + j) * 128 + col, (1ull << 32) | v[j]);
+                    put_partial(v, j0);
                     continue;
                 }
-                if (C::kSplit) {
-                    bool waiting_ok = true;
-                    for (int bb = b_lo + 1; bb <= b_hi; ++bb) {
-                        unsigned long long* src = partials64 + (size_t)bb * (32 * 128) + col;
-#pragma unroll
-                        for (int jb = 0; jb < CH; jb += 8) {
-                            if (j0 + jb >= nrows) break;                       // warp-uniform
-                            unsigned long long w[8];
-#pragma unroll
-                            for (int i = 0; i < 8; ++i)
-                                if (j0 + jb + i < nrows) w[i] = ptx::ld_relaxed_gpu_u64(src + (j0 + jb + i) * 128);
-#pragma unroll
-                            for (int i = 0; i < 8; ++i) {
-                                if (j0 + jb + i < nrows) {
-                                    for (uint32_t spins = 0; (uint32_t)(w[i] >> 32) != 1u && waiting_ok; ++spins) {
-                                        if (spins >= ptx::kSpinLimit) {        // a contributor never delivered: report, stop waiting
-                                            atomicExch(p.status, 34);
-                                            waiting_ok = false;
-                                            break;
-                                        }
-                                        __nanosleep(64);
-                                        w[i] = ptx::ld_relaxed_gpu_u64(src + (j0 + jb + i) * 128);
-                                    }
-                                    v[jb + i] = __float_as_uint(__uint_as_float(v[jb + i]) + __uint_as_float((uint32_t)w[i]));
-                                    ptx::st_relaxed_gpu_u64(src + (j0 + jb + i) * 128, 0ull);
-                                }
-                            }
-                        }
-                    }
-                }
+                if (C::kSplit && b_hi > b_lo) add_partials(v, j0);
                 if (col_ok) {
 #pragma unroll
                     for (int j = 0; j < CH; ++j) {
@@ -903,6 +932,8 @@ bool encode_2d(CUtensorMap* out, const void* base, CUtensorMapDataType dt, int e
                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+constexpr long long kPartialWords = 148LL * 4 * 32 * 128;      // 64-bit words of partial tiles in the workspace (capi.cu sizes it)
+
 template <int BITS, bool SPARSE, int NT, bool PAIR>
 int launch_nt(const UmmaParams& p, const __half* x, int n_groups, cudaStream_t stream, cudaError_t* cuda_err) {
     using F = UFormat<BITS, SPARSE>;
@@ -971,7 +1002,8 @@ int launch_nt(const UmmaParams& p, const __half* x, int n_groups, cudaStream_t s
             max_clusters[dev] = n;
         }
         long long clusters = max_clusters[dev];
-        const long long work = (long long)p.MTILES * ((p.CT + 1) / 2);
+        const long long work = (long long)p.MTILES * ((p.CT + 1) / 2) * (C::kSplit ? p.U : 1);
+        if (C::kSplit && clusters > kPartialWords / C::kSlotElems / 2) clusters = kPartialWords / C::kSlotElems / 2;
         if (clusters > work) clusters = work;
         cfg.gridDim = dim3((unsigned)(2 * clusters), 1, 1);
         e = cudaLaunchKernelEx(&cfg, kern, tm, p);
@@ -982,7 +1014,7 @@ int launch_nt(const UmmaParams& p, const __half* x, int n_groups, cudaStream_t s
     long long grid = (long long)sm_count[dev] * ctas_per_sm[dev];
     const long long work = C::kSplit ? n_tiles * p.U : n_tiles;
     if (grid > work) grid = work;
-    if (C::kSplit && grid > 148 * 4) grid = 148 * 4;        // the scratch holds one partial tile per CTA for this many CTAs
+    if (C::kSplit && grid > kPartialWords / C::kSlotElems) grid = kPartialWords / C::kSlotElems;   // one partial tile per CTA in the scratch
     kern<<<(int)grid, C::kThreads, smem, stream>>>(tm, p);
     e = cudaGetLastError();
     if (e != cudaSuccess) { *cuda_err = e; return I4MM_ERR_LAUNCH; }
