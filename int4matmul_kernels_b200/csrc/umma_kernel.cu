@@ -278,9 +278,15 @@ struct Barriers {
     unsigned long long d_full, d_empty;
 };
 
-__device__ __forceinline__ long long range_lo(long long T, long long G, long long b) { return (T * b) / G; }
+// Non-negative quotient; 64-bit division is a ~500-cycle subroutine on the GPU, so the 32-bit one is used whenever the
+// operands allow it (practically always: unit counts are far below 2^32).
+__device__ __forceinline__ long long div_nn(long long a, long long b) {
+    if (((unsigned long long)a | (unsigned long long)b) >> 32) return a / b;
+    return (long long)((uint32_t)a / (uint32_t)b);
+}
+__device__ __forceinline__ long long range_lo(long long T, long long G, long long b) { return div_nn(T * b, G); }
 __device__ __forceinline__ int range_owner(long long T, long long G, long long t) {
-    return (int)(((t + 1) * G + T - 1) / T - 1);
+    return (int)(div_nn((t + 1) * G + T - 1, T) - 1);
 }
 
 struct TensorMaps {
@@ -407,7 +413,7 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
             uint32_t si = 0, ws = 0, wph = 0;
             bool ok = true;
             for (long long t = t_lo; t < t_hi && ok;) {
-                const long long tile = t / U;                      // one 64-bit division per segment, none per unit
+                const long long tile = div_nn(t, U);                      // one 64-bit division per segment, none per unit
                 const int u0 = (int)(t - tile * U);
                 const int u1 = (int)min(U, u0 + (t_hi - t));
                 const int ct = tile_ct(tile);
@@ -436,7 +442,7 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
             uint32_t ws = 0, wph = 0;
             bool ok = true;
             for (long long t = t_lo; t < t_hi && ok;) {
-                const long long tile = t / U;
+                const long long tile = div_nn(t, U);
                 const int u0 = (int)(t - tile * U);
                 const int u1 = (int)min(U, u0 + (t_hi - t));
                 const int ct = tile_ct(tile);
@@ -458,7 +464,7 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
             uint32_t s = 0, ph = 0;
             bool ok = true;
             for (long long t = t_lo; t < t_hi && ok;) {
-                const long long tile = t / U;
+                const long long tile = div_nn(t, U);
                 const int u0 = (int)(t - tile * U);
                 const int u1 = (int)min(U, u0 + (t_hi - t));
                 const int mt = tile_mt(tile);
@@ -491,7 +497,7 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
             bool ok = true;
             if (PAIR && rank != 0) t_lo = t_hi;              // the leader issues for both CTAs
             for (long long t = t_lo; t < t_hi && ok;) {
-                const long long tile = t / U;
+                const long long tile = div_nn(t, U);
                 const int u0 = (int)(t - tile * U);
                 const int u1 = (int)min(U, u0 + (t_hi - t));
                 TRACE(3, (int)seg, 4);
@@ -766,7 +772,7 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
             uint32_t seg = 0;
             bool first_segment = true;
             for (long long t = t_lo; t < t_hi;) {
-                const long long tile = t / U;
+                const long long tile = div_nn(t, U);
                 const int u0 = (int)(t - tile * U);
                 const int u1 = (int)min(U, u0 + (t_hi - t));
                 if (!epilogue(seg, tile, u0, u1, first_segment)) break;
@@ -794,7 +800,7 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
             bool ok = true;
             bool first_segment = true;
             for (long long t = t_lo; t < t_hi && ok;) {
-                const long long tile = t / U;
+                const long long tile = div_nn(t, U);
                 const int u0 = (int)(t - tile * U);
                 const int u1 = (int)min(U, u0 + (t_hi - t));
                 // this warpgroup's units of the segment: those whose stage index is congruent to wg modulo kWG
