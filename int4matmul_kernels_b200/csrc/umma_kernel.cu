@@ -236,12 +236,12 @@ struct Cfg {
     // packed-weight ring (128 k per stage).  Few rows: the kernel streams weights from HBM, and the ring has to
     // cover the DRAM latency; many rows: weights are a trickle next to the activation tiles
     static constexpr bool kStream = NT <= 32;                         // weight-streaming shapes: one CTA per SM with everything doubled
-    // NT = 128 (65..128 rows): an MMA of N = 128 takes half as long as the dequantisation of its weights with two
-    // warpgroups, so this shape gets four as well, and a deeper ring
-    static constexpr bool kDequantBound = NT == 128;
+    // NT = 128..192: an MMA of N <= 192 takes 512..768 cycles per 128 k, the dequantisation of its weights with two
+    // warpgroups ~1400, so these shapes get four warpgroups as well, and a deeper weight ring
+    static constexpr bool kDequantBound = NT >= 128 && NT <= 192;
     static constexpr int kWStages = kStream ? 16 : NT <= 64 ? 8 : kDequantBound ? 6 : 3;
     static constexpr int kWG = (kStream || kDequantBound) ? 4 : 2;    // dequant warpgroups (4 warps each), taking units in turn
-    static constexpr int kABStages = kStream ? 6 : kDequantBound ? 4 : 3;   // ring of (A in tensor memory, activation tile in shared memory) pairs, 128 k per stage
+    static constexpr int kABStages = kStream ? 6 : NT == 128 ? 4 : 3;   // ring of (A in tensor memory, activation tile in shared memory) pairs, 128 k per stage
     static constexpr bool kEpiWarps = NT >= 128 || kStream;           // a warpgroup of its own for the epilogue (else dequant warpgroup 0 does it)
     static constexpr bool kEpiTransposed = NT >= 128;                 // epilogue stores go through a shared-memory transposition tile
     static constexpr bool kEpiHandoff = kStream;                      // the MMA warp waits for the accumulator and wakes the epilogue warps (named barrier)
