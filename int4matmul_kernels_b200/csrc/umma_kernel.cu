@@ -573,7 +573,7 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
         // =========================== dequant warpgroups; epilogue warps ===========================
         // Accumulator of one finished segment -> fp16 rows of `out`, or a partial tile for the split-K reduction.
         // Run by 4 warps whose index modulo 4 selects the 32 tensor-memory lanes (= weight columns) they may read.
-        auto epilogue = [&](uint32_t seg, long long tile, int u0, int u1, bool first_segment) -> bool {
+        auto epilogue = [&](uint32_t seg, long long tile, int u0, int u1) -> bool {
             const int mt = tile_mt(tile), ct = tile_ct(tile);
             const int col = (warp & 3) * 32 + lane;
             const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
@@ -607,7 +607,6 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
                 b_hi = range_owner(T, G, lo_t + U - 1);
                 if ((int)b != b_lo) slot = partials64 + (size_t)(PAIR ? b * 2 + rank : b) * C::kSlotElems;
             }
-            (void)first_segment;
             // leaves accumulator rows j0 .. j0 + n - 1 of this lane's column in this CTA's slot
             auto put_partial = [&](auto& v, int j0) {
                 constexpr int CNT = (int)(sizeof(v) / sizeof(uint32_t));
@@ -770,15 +769,13 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
         } else if (C::kEpiWarps && warp >= kEpiWarp0) {
             // ----- dedicated epilogue warps: one pass per segment -----
             uint32_t seg = 0;
-            bool first_segment = true;
             for (long long t = t_lo; t < t_hi;) {
                 const long long tile = div_nn(t, U);
                 const int u0 = (int)(t - tile * U);
                 const int u1 = (int)min(U, u0 + (t_hi - t));
-                if (!epilogue(seg, tile, u0, u1, first_segment)) break;
+                if (!epilogue(seg, tile, u0, u1)) break;
                 ++seg;
                 t += u1 - u0;
-                first_segment = false;
             }
         } else {
             // ----- dequant warps -----
@@ -798,7 +795,6 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
                 }
             };
             bool ok = true;
-            bool first_segment = true;
             for (long long t = t_lo; t < t_hi && ok;) {
                 const long long tile = div_nn(t, U);
                 const int u0 = (int)(t - tile * U);
@@ -872,11 +868,10 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
                 }
                 if (!ok) break;
                 if (C::kDeferArrive && pending >= 0) { announce(pending); pending = -1; }
-                if (!C::kEpiWarps && wg == 0) ok = epilogue(seg, tile, u0, u1, first_segment);
+                if (!C::kEpiWarps && wg == 0) ok = epilogue(seg, tile, u0, u1);
                 ++seg;
                 si0 += (uint32_t)(u1 - u0);
                 t += u1 - u0;
-                first_segment = false;
             }
         }
     }
