@@ -64,6 +64,8 @@ struct UmmaParams {
     int CT;              // column tiles: ceil(S / 128)
     int MTILES;          // row tiles: ceil(rows / NT)
     int accumulate;
+    int kparts;          // > 1: every tile's K range is cut into this many parts, one CTA (pair) each, fp32 partial outputs
+                         // go to the scratch as (part, row, S) and kparts_reduce_kernel sums them (64..128-row tiles only)
     GroupDiv gdiv;
 };
 
@@ -397,9 +399,15 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
     auto tile_ct = [&](long long tile) -> int { return (int)(tile % CTd) * (PAIR ? 2 : 1) + (int)rank; };
     auto tile_mt = [&](long long tile) -> int { return (int)(tile / CTd); };
     long long t_lo, t_hi;
+    const int kpart = p.kparts > 1 ? (int)(b % p.kparts) : 0;
     if (C::kSplit) {
         t_lo = range_lo(n_tiles * U, G, b);
         t_hi = range_lo(n_tiles * U, G, b + 1);
+    } else if (p.kparts > 1) {
+        // the grid is exactly tiles x parts: one part of one tile per CTA (pair)
+        const long long tile = b / p.kparts;
+        t_lo = tile * U + (U * kpart) / p.kparts;
+        t_hi = tile * U + (U * (kpart + 1)) / p.kparts;
     } else {
         t_lo = range_lo(n_tiles, G, b) * U;
         t_hi = range_lo(n_tiles, G, b + 1) * U;
@@ -607,6 +615,15 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
                 b_hi = range_owner(T, G, lo_t + U - 1);
                 if ((int)b != b_lo) slot = partials64 + (size_t)(PAIR ? b * 2 + rank : b) * C::kSlotElems;
             }
+            // K parts: fp32 rows j0 .. of this lane's column into the (part, row, S) scratch; the reduce kernel sums the parts
+            auto put_kpart = [&](auto& v, int j0) {
+                constexpr int CNT = (int)(sizeof(v) / sizeof(uint32_t));
+                if (!col_ok) return;
+#pragma unroll
+                for (int j = 0; j < CNT; ++j)
+                    if (j0 + j < nrows)
+                        p.partials[((size_t)kpart * p.rows + row0 + j0 + j) * p.S + scol] = __uint_as_float(v[j]);
+            };
             // leaves accumulator rows j0 .. j0 + n - 1 of this lane's column in this CTA's slot
             auto put_partial = [&](auto& v, int j0) {
                 constexpr int CNT = (int)(sizeof(v) / sizeof(uint32_t));
@@ -677,6 +694,10 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
                             }
                             if (b_hi > b_lo) add_partials(v, j0);
                         }
+                        if (p.kparts > 1) {
+                            put_kpart(v, j0);
+                            continue;
+                        }
 #pragma unroll
                         for (int j = 0; j < 16; ++j)
                             ptx::sts16(stage + (j0 - eg * kShare + j) * 256 + col * 2,
@@ -684,7 +705,7 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
                     }
                     ptx::named_bar_sync(bar_id, 128);
 #pragma unroll 1
-                    for (int idx = t128; idx < (slot ? 0 : kShare * 16); idx += 128) {   // 16-byte chunks: row = idx / 16, chunk = idx % 16
+                    for (int idx = t128; idx < ((slot || p.kparts > 1) ? 0 : kShare * 16); idx += 128) {   // 16-byte chunks: row = idx / 16, chunk = idx % 16
                         const int m = eg * kShare + (idx >> 4), c8 = (idx & 15) * 8;
                         if (m < nrows && ct * 128 + c8 < p.S) {
                             const uint4 q = ptx::lds128(stage + (idx >> 4) * 256 + c8 * 2);
@@ -712,6 +733,10 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
                             continue;
                         }
                         if (b_hi > b_lo) add_partials(v, j0);
+                    }
+                    if (p.kparts > 1) {
+                        put_kpart(v, j0);
+                        continue;
                     }
 #pragma unroll
                     for (int j = 0; j < 16; ++j)
@@ -746,6 +771,10 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
                     continue;
                 }
                 if (C::kSplit && b_hi > b_lo) add_partials(v, j0);
+                if (p.kparts > 1) {
+                    put_kpart(v, j0);
+                    continue;
+                }
                 if (col_ok) {
 #pragma unroll
                     for (int j = 0; j < CH; ++j) {
@@ -895,6 +924,28 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
 #endif
 }
 
+// Sums the K parts written by umma_kernel (fp32, (part, row, S)) in part order, rounds once to fp16, and puts the
+// scratch back to all-zero (the split-K reduction of the few-row shapes relies on that).  8 columns per thread.
+__global__ void kparts_reduce_kernel(float* __restrict__ parts, __half* __restrict__ out, int rows, int S, int kparts) {
+    const long long n8 = (long long)rows * S / 8;
+    const size_t stride = (size_t)rows * S;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (long long)gridDim.x * blockDim.x) {
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int f = 0; f < kparts; ++f) {
+            float4* src = reinterpret_cast<float4*>(parts + f * stride + i * 8);
+            const float4 a = src[0], c = src[1];
+            acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w;
+            acc[4] += c.x; acc[5] += c.y; acc[6] += c.z; acc[7] += c.w;
+            src[0] = make_float4(0.f, 0.f, 0.f, 0.f);
+            src[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        __half2 h[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) h[j] = __floats2half2_rn(acc[2 * j], acc[2 * j + 1]);
+        *reinterpret_cast<uint4*>(out + i * 8) = *reinterpret_cast<uint4*>(h);
+    }
+}
+
 // ---- host side -------------------------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -935,8 +986,31 @@ bool encode_2d(CUtensorMap* out, const void* base, CUtensorMapDataType dt, int e
 
 constexpr long long kPartialWords = 148LL * 4 * 32 * 128;      // 64-bit words of partial tiles in the workspace (capi.cu sizes it)
 
+// 64..128-row tiles (one row tile) whose column tiles fill less than half of the GPU: cut K into parts so that
+// tiles x parts CTAs (pairs) run, as long as every part keeps at least 4 stages and the partial outputs fit the scratch.
+int choose_kparts(long long capacity, long long tiles, int U, long long rows, long long S) {
+    if (tiles <= 0 || tiles * 2 > capacity) return 1;
+    long long f = capacity / tiles;
+    if (f > 8) f = 8;
+    if (f > U / 4) f = U / 4;
+    while (f > 1 && f * rows * S * 4 > kPartialWords * 8) --f;
+    return f < 2 ? 1 : (int)f;
+}
+
+int launch_kparts_reduce(const UmmaParams& p, cudaStream_t stream, cudaError_t* cuda_err) {
+    const long long n8 = (long long)p.rows * p.S / 8;
+    long long blocks = (n8 + 255) / 256;
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    kparts_reduce_kernel<<<(int)blocks, 256, 0, stream>>>(p.partials, p.out, p.rows, p.S, p.kparts);
+    const cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) { *cuda_err = e; return I4MM_ERR_LAUNCH; }
+    return I4MM_OK;
+}
+
 template <int BITS, bool SPARSE, int NT, bool PAIR>
-int launch_nt(const UmmaParams& p, const __half* x, int n_groups, cudaStream_t stream, cudaError_t* cuda_err) {
+int launch_nt(const UmmaParams& p_in, const __half* x, int n_groups, cudaStream_t stream, cudaError_t* cuda_err) {
+    UmmaParams p = p_in;
+    p.kparts = 1;
     using F = UFormat<BITS, SPARSE>;
     using C = Cfg<NT>;
     constexpr int kBStageBytes = 2 * (PAIR ? NT / 2 : NT) * 128;
@@ -1003,22 +1077,29 @@ int launch_nt(const UmmaParams& p, const __half* x, int n_groups, cudaStream_t s
             max_clusters[dev] = n;
         }
         long long clusters = max_clusters[dev];
-        const long long work = (long long)p.MTILES * ((p.CT + 1) / 2) * (C::kSplit ? p.U : 1);
+        const long long tiles2 = (long long)p.MTILES * ((p.CT + 1) / 2);
+        if (NT <= 128 && !C::kSplit && p.MTILES == 1 && !p.accumulate)
+            p.kparts = choose_kparts(clusters, tiles2, p.U, p.rows, p.S);
+        const long long work = p.kparts > 1 ? tiles2 * p.kparts : tiles2 * (C::kSplit ? p.U : 1);
         if (C::kSplit && clusters > kPartialWords / C::kSlotElems / 2) clusters = kPartialWords / C::kSlotElems / 2;
-        if (clusters > work) clusters = work;
+        if (clusters > work || p.kparts > 1) clusters = work;
         cfg.gridDim = dim3((unsigned)(2 * clusters), 1, 1);
         e = cudaLaunchKernelEx(&cfg, kern, tm, p);
         if (e != cudaSuccess) { *cuda_err = e; return I4MM_ERR_LAUNCH; }
+        if (p.kparts > 1) return launch_kparts_reduce(p, stream, cuda_err);
         return I4MM_OK;
     }
     const long long n_tiles = (long long)p.MTILES * p.CT;
     long long grid = (long long)sm_count[dev] * ctas_per_sm[dev];
-    const long long work = C::kSplit ? n_tiles * p.U : n_tiles;
-    if (grid > work) grid = work;
+    if (NT >= 64 && NT <= 128 && !C::kSplit && p.MTILES == 1 && !p.accumulate)
+        p.kparts = choose_kparts(grid, n_tiles, p.U, p.rows, p.S);
+    const long long work = p.kparts > 1 ? n_tiles * p.kparts : C::kSplit ? n_tiles * p.U : n_tiles;
+    if (grid > work || p.kparts > 1) grid = work;
     if (C::kSplit && grid > kPartialWords / C::kSlotElems) grid = kPartialWords / C::kSlotElems;   // one partial tile per CTA in the scratch
     kern<<<(int)grid, C::kThreads, smem, stream>>>(tm, p);
     e = cudaGetLastError();
     if (e != cudaSuccess) { *cuda_err = e; return I4MM_ERR_LAUNCH; }
+    if (p.kparts > 1) return launch_kparts_reduce(p, stream, cuda_err);
     return I4MM_OK;
 }
 

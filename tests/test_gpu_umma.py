@@ -118,6 +118,25 @@ def test_cta_pairs_with_odd_and_even_column_tile_counts(s):
     assert_parity(got, want, bound, f"pairs S={s}")
 
 
+@pytest.mark.parametrize("fmt", FORMATS, ids=fmt_id)
+@pytest.mark.parametrize("m", [40, 64, 100, 128])
+@pytest.mark.parametrize("path", [P, capi.PATH_TCGEN05_SINGLE_CTA])
+def test_k_parts_for_shapes_with_few_column_tiles(fmt, m, path):
+    """33..128 rows and few column tiles: K is cut into parts (one CTA or CTA pair each) whose fp32 partial outputs a
+    second kernel sums in part order; afterwards the few-row split-K path must still find its scratch all-zero."""
+    bits, sparse = fmt
+    p = oracle.make_problem(bits, 2048, 320, m, 128, sparse=sparse, seed=700 + m)
+    got = run_problem(p, path=path)
+    want, _, bound = oracle.expected(p)
+    assert_parity(got, want, bound, f"k-parts rows={m} {fmt}")
+    again = run_problem(p, path=path)
+    assert np.array_equal(got.view(np.uint16), again.view(np.uint16))
+    p1 = oracle.make_problem(bits, 2048, 320, 1, 128, sparse=sparse, seed=800 + m)
+    got1 = run_problem(p1, path=P)
+    want1, _, bound1 = oracle.expected(p1, outs_in=np.zeros((1, 1, 320), np.float16))
+    assert_parity(got1, want1, bound1, f"matvec after k-parts {fmt}")
+
+
 def test_no_device_timeouts_recorded():
     ws = ops.workspace(torch.device("cuda", torch.cuda.current_device()), torch.cuda.current_stream())
     assert capi.load().i4mm_device_status(ws.data_ptr(), torch.cuda.current_stream().cuda_stream) == capi.OK
