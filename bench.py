@@ -303,14 +303,22 @@ def run_stack(args):
                 step()
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
+            n0 = capi.load().i4mm_launch_count()
             with torch.cuda.graph(graph, stream=side):
                 for _ in range(args.steps):
                     out = step()
+            k_launches = capi.load().i4mm_launch_count() - n0      # kernels of ours in the K captured steps
             graph.replay()
             torch.cuda.synchronize()
         except Exception as e:
             print(f"[bench] CUDA graph capture unavailable ({type(e).__name__}: {e}); timing direct launches", file=sys.stderr)
             graph = None
+
+    if graph is None:
+        n0 = capi.load().i4mm_launch_count()
+        for _ in range(args.steps):
+            step()
+        k_launches = capi.load().i4mm_launch_count() - n0
 
     def run_steps():
         if graph is not None:
@@ -381,7 +389,7 @@ def run_stack(args):
             cpu_baseline=None,
             e2e=dict(value=units / (ms_e2e / args.steps / 1e3), unit=unit, h2d_bytes_per_step=h_host.numel() * 2,
                      d2h_bytes_per_step=out_host.numel() * 2, ms_per_step=ms_e2e / args.steps),
-            clocks=clocks.summary(), gpu_launches=args.steps * cfg.layers * 4)))
+            clocks=clocks.summary(), gpu_launches=int(k_launches))))
     if world > 1:
         dist.destroy_process_group()
 
@@ -466,9 +474,11 @@ def main():
                 step(0)                                   # allocates this stream's scratch outside the capture
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
+            n0 = capi.load().i4mm_launch_count()
             with torch.cuda.graph(graph, stream=side):
                 for i in range(args.steps):
                     step(i)
+            k_launches = capi.load().i4mm_launch_count() - n0      # kernels of ours in the K captured steps
             graph.replay()
             torch.cuda.synchronize()
         except Exception as e:                            # capture is an optimisation of the harness only
@@ -479,6 +489,12 @@ def main():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
+
+    if graph is None:
+        n0 = capi.load().i4mm_launch_count()
+        for i in range(args.steps):
+            step(i)
+        k_launches = capi.load().i4mm_launch_count() - n0
 
     def run_steps():
         if graph is not None:
@@ -586,7 +602,7 @@ def main():
                                 sharding=f"S columns over {world} GPU(s)", l2="rotating %d weight copies (> 2x L2)" % copies,
                                 timed_as="one CUDA graph of the K steps" if graph is not None else "K direct launches"),
                     roofline=roofline, cpu_baseline=cpu, reference_cuda=ref_gpu, e2e=e2e, clocks=clocks.summary(),
-                    gpu_launches=args.steps * launches_per_step)
+                    gpu_launches=int(k_launches))
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()

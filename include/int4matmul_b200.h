@@ -49,6 +49,9 @@ const char* i4mm_status_string(int status);
 int i4mm_last_cuda_error(void);
 /* Library version: major*10000 + minor*100 + patch. */
 int i4mm_version(void);
+/* Kernels this library has launched in this process so far, over all entry points (a multiply is one launch,
+ * or two where it cuts K into parts and reduces them).  For accounting in benchmarks; no reference counterpart. */
+unsigned long long i4mm_launch_count(void);
 
 /*
  * Bytes of device scratch the two multiply entries need.  The scratch holds the per-CTA partial tiles

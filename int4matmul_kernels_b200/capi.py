@@ -23,6 +23,7 @@ _SIGNATURES = {
     "i4mm_status_string": (ctypes.c_char_p, [ctypes.c_int]),
     "i4mm_last_cuda_error": (ctypes.c_int, []),
     "i4mm_version": (ctypes.c_int, []),
+    "i4mm_launch_count": (ctypes.c_ulonglong, []),
     "i4mm_workspace_bytes": (ctypes.c_size_t, []),
     "i4mm_quant_matmul": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, ctypes.c_int,
                                          ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,

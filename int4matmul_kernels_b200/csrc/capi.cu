@@ -2,9 +2,13 @@
 // The declarations and the reference interfaces they replace are in include/int4matmul_b200.h.
 #include "../../include/int4matmul_b200.h"
 
+#include <atomic>
+
 #include "common.cuh"
 
 namespace i4mm {
+static std::atomic<unsigned long long> g_launches{0};
+void count_launch(int n) { g_launches.fetch_add((unsigned long long)n); }
 cudaError_t stream_launch(int bits, bool sparse, StreamParams p, int total_rows, int ctas, cudaStream_t stream);
 cudaError_t sparse_pack_launch(void* wt_out, void* msk_out, const void* wt_in, const void* msk_in,
                                int S, int N, void* violations, cudaStream_t stream);
@@ -60,6 +64,8 @@ const char* i4mm_status_string(int status) {
 int i4mm_last_cuda_error(void) { return g_last_cuda_error; }
 
 int i4mm_version(void) { return 100; }
+
+unsigned long long i4mm_launch_count(void) { return i4mm::g_launches.load(); }
 
 size_t i4mm_workspace_bytes(void) { return kCounterBytes + kPartialBytes; }
 

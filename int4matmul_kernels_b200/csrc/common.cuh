@@ -92,4 +92,7 @@ struct StreamParams {
     GroupDiv gdiv;
 };
 
+// Counts kernel launches of this library in this process (read through i4mm_launch_count); defined in capi.cu.
+void count_launch(int n = 1);
+
 }  // namespace i4mm

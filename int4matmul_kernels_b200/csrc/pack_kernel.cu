@@ -73,6 +73,7 @@ cudaError_t sparse_pack_launch(void* wt_out, void* msk_out, const void* wt_in, c
     dim3 grid((nblk + kPackBlks - 1) / kPackBlks, (S + kPackCols - 1) / kPackCols);
     sparse_pack_kernel<<<grid, kPackCols * kPackBlks, 0, stream>>>(
         (uint32_t*)wt_out, (uint32_t*)msk_out, (const uint8_t*)wt_in, (const uint8_t*)msk_in, S, N, (int*)violations);
+    count_launch();
     return cudaGetLastError();
 }
 
@@ -82,6 +83,7 @@ cudaError_t check_mask_launch(const void* mask, size_t count, void* violations, 
     size_t blocks = (count + threads - 1) / threads;
     if (blocks > 148 * 8) blocks = 148 * 8;
     check_mask_kernel<<<(int)blocks, threads, 0, stream>>>((const uint32_t*)mask, count, (int*)violations);
+    count_launch();
     return cudaGetLastError();
 }
 

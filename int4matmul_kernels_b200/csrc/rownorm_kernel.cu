@@ -77,6 +77,7 @@ cudaError_t rownorm_launch(int mode, void* y, const void* a, const void* b, cons
         case 2: rownorm_kernel<2><<<grid, block, 0, stream>>>(yy, aa, bb, cc, width, sa, sb, sc); break;
         default: rownorm_kernel<3><<<grid, block, 0, stream>>>(yy, aa, bb, cc, width, sa, sb, sc); break;
     }
+    count_launch();
     return cudaGetLastError();
 }
 

@@ -693,6 +693,7 @@ static cudaError_t launch_one(const StreamParams& p, int max_ctas, cudaStream_t 
     if (grid > max_ctas) grid = max_ctas;
     if (grid > T) grid = T;
     kern<<<(int)grid, kStreamThreads, smem, stream>>>(p);
+    count_launch();
     return cudaGetLastError();
 }
 

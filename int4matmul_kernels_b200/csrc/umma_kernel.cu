@@ -1002,6 +1002,7 @@ int launch_kparts_reduce(const UmmaParams& p, cudaStream_t stream, cudaError_t* 
     long long blocks = (n8 + 255) / 256;
     if (blocks > 148 * 8) blocks = 148 * 8;
     kparts_reduce_kernel<<<(int)blocks, 256, 0, stream>>>(p.partials, p.out, p.rows, p.S, p.kparts);
+    count_launch();
     const cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) { *cuda_err = e; return I4MM_ERR_LAUNCH; }
     return I4MM_OK;
@@ -1086,6 +1087,7 @@ int launch_nt(const UmmaParams& p_in, const __half* x, int n_groups, cudaStream_
         cfg.gridDim = dim3((unsigned)(2 * clusters), 1, 1);
         e = cudaLaunchKernelEx(&cfg, kern, tm, p);
         if (e != cudaSuccess) { *cuda_err = e; return I4MM_ERR_LAUNCH; }
+        count_launch();
         if (p.kparts > 1) return launch_kparts_reduce(p, stream, cuda_err);
         return I4MM_OK;
     }
@@ -1099,6 +1101,7 @@ int launch_nt(const UmmaParams& p_in, const __half* x, int n_groups, cudaStream_
     kern<<<(int)grid, C::kThreads, smem, stream>>>(tm, p);
     e = cudaGetLastError();
     if (e != cudaSuccess) { *cuda_err = e; return I4MM_ERR_LAUNCH; }
+    count_launch();
     if (p.kparts > 1) return launch_kparts_reduce(p, stream, cuda_err);
     return I4MM_OK;
 }
