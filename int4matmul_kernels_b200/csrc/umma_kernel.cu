@@ -65,7 +65,7 @@ struct UmmaParams {
     int MTILES;          // row tiles: ceil(rows / NT)
     int accumulate;
     int kparts;          // > 1: every tile's K range is cut into this many parts, one CTA (pair) each, fp32 partial outputs
-                         // go to the scratch as (part, row, S) and kparts_reduce_kernel sums them (64..128-row tiles only)
+                         // go to the scratch as (part, row, S) and kparts_reduce_kernel sums them (more than 32 rows only)
     GroupDiv gdiv;
 };
 
@@ -986,7 +986,7 @@ bool encode_2d(CUtensorMap* out, const void* base, CUtensorMapDataType dt, int e
 
 constexpr long long kPartialWords = 148LL * 4 * 32 * 128;      // 64-bit words of partial tiles in the workspace (capi.cu sizes it)
 
-// 64..128-row tiles (one row tile) whose column tiles fill less than half of the GPU: cut K into parts so that
+// More than 32 rows and tiles that fill less than half of the GPU: cut K into parts so that
 // tiles x parts CTAs (pairs) run, as long as every part keeps at least 4 stages and the partial outputs fit the scratch.
 int choose_kparts(long long capacity, long long tiles, int U, long long rows, long long S) {
     if (tiles <= 0 || tiles * 2 > capacity) return 1;
@@ -1079,7 +1079,7 @@ int launch_nt(const UmmaParams& p_in, const __half* x, int n_groups, cudaStream_
         }
         long long clusters = max_clusters[dev];
         const long long tiles2 = (long long)p.MTILES * ((p.CT + 1) / 2);
-        if (NT <= 128 && !C::kSplit && p.MTILES == 1 && !p.accumulate)
+        if (!C::kSplit && !p.accumulate)
             p.kparts = choose_kparts(clusters, tiles2, p.U, p.rows, p.S);
         const long long work = p.kparts > 1 ? tiles2 * p.kparts : tiles2 * (C::kSplit ? p.U : 1);
         if (C::kSplit && clusters > kPartialWords / C::kSlotElems / 2) clusters = kPartialWords / C::kSlotElems / 2;
@@ -1093,7 +1093,7 @@ int launch_nt(const UmmaParams& p_in, const __half* x, int n_groups, cudaStream_
     }
     const long long n_tiles = (long long)p.MTILES * p.CT;
     long long grid = (long long)sm_count[dev] * ctas_per_sm[dev];
-    if (NT >= 64 && NT <= 128 && !C::kSplit && p.MTILES == 1 && !p.accumulate)
+    if (!C::kSplit && !p.accumulate)
         p.kparts = choose_kparts(grid, n_tiles, p.U, p.rows, p.S);
     const long long work = p.kparts > 1 ? n_tiles * p.kparts : C::kSplit ? n_tiles * p.U : n_tiles;
     if (grid > work || p.kparts > 1) grid = work;

@@ -119,10 +119,10 @@ def test_cta_pairs_with_odd_and_even_column_tile_counts(s):
 
 
 @pytest.mark.parametrize("fmt", FORMATS, ids=fmt_id)
-@pytest.mark.parametrize("m", [40, 64, 100, 128])
+@pytest.mark.parametrize("m", [40, 64, 100, 128, 300, 520])
 @pytest.mark.parametrize("path", [P, capi.PATH_TCGEN05_SINGLE_CTA])
 def test_k_parts_for_shapes_with_few_column_tiles(fmt, m, path):
-    """33..128 rows and few column tiles: K is cut into parts (one CTA or CTA pair each) whose fp32 partial outputs a
+    """More than 32 rows and few tiles: K is cut into parts (one CTA or CTA pair each) whose fp32 partial outputs a
     second kernel sums in part order; afterwards the few-row split-K path must still find its scratch all-zero."""
     bits, sparse = fmt
     p = oracle.make_problem(bits, 2048, 320, m, 128, sparse=sparse, seed=700 + m)
