@@ -18,7 +18,7 @@
 //   epilogue          4 warps read the accumulator (tcgen05.ld), convert to fp16 and store; a warpgroup of its own
 //                     except for 33..64 rows, where dequant warpgroup 0 does it
 //
-// Configurations (Cfg<NT>): NT <= 32 rows stream the weights once from HBM - one CTA per SM, 4 dequant warpgroups,
+// Configurations (Cfg<NT, PAIR>): NT <= 32 rows stream the weights once from HBM - one CTA per SM, 4 dequant warpgroups,
 // 16 weight stages, 6 A / activation stages, and the (tile, unit) space cut into equal ranges per CTA (split-K over
 // the whole GPU, partial tiles summed through scratch in a fixed order).  NT = 64: two CTAs per SM, whole tiles.
 // NT >= 128: one CTA per SM, whole tiles, epilogue stores transposed through shared memory; by default launched as
@@ -233,17 +233,25 @@ struct WStage {     // one stage of the packed-weight ring: 128 k = two 64-k hal
 constexpr int kMaxWStages = 16;
 constexpr int kMaxABStages = 6;
 
-template <int NT>
+template <int NT, bool PAIR>
 struct Cfg {
     // packed-weight ring (128 k per stage).  Few rows: the kernel streams weights from HBM, and the ring has to
     // cover the DRAM latency; many rows: weights are a trickle next to the activation tiles
     static constexpr bool kStream = NT <= 32;                         // weight-streaming shapes: one CTA per SM with everything doubled
     // NT = 128..192: an MMA of N <= 192 takes 512..768 cycles per 128 k, the dequantisation of its weights with two
     // warpgroups ~1400, so these shapes get four warpgroups as well, and a deeper weight ring
-    static constexpr bool kDequantBound = NT >= 128 && NT <= 192;
+    // (single CTAs have the shared memory for the 4 A / activation stages that four warpgroups need only at NT = 128)
+    static constexpr bool kDequantBound = NT == 128 || (PAIR && NT >= 128 && NT <= 192);
+    // A stage of either ring is waited for by parity, which tells a completed phase only from the one before it.
+    // Where the weight stages are not a multiple of the warpgroups, consecutive uses of a stage belong to different
+    // warpgroups, and one could poll for a stage's next fill while the previous one, meant for another warpgroup, has
+    // not landed yet (tensor-map copies may complete out of order) and take the stale phase for its own: there the
+    // dequant warps first wait, like the producer, until the previous use has been released (kWGuard).  And there
+    // are at least as many A stages as warpgroups (checked in the kernel).
     static constexpr int kWStages = kStream ? 16 : NT <= 64 ? 8 : kDequantBound ? 6 : 3;
     static constexpr int kWG = (kStream || kDequantBound) ? 4 : 2;    // dequant warpgroups (4 warps each), taking units in turn
     static constexpr int kABStages = kStream ? 6 : NT == 128 ? 4 : 3;   // ring of (A in tensor memory, activation tile in shared memory) pairs, 128 k per stage
+    static constexpr bool kWGuard = kWStages % kWG != 0;
     static constexpr bool kEpiWarps = NT >= 128 || kStream;           // a warpgroup of its own for the epilogue (else dequant warpgroup 0 does it)
     static constexpr bool kEpiTransposed = NT >= 128;                 // epilogue stores go through a shared-memory transposition tile
     static constexpr bool kEpiHandoff = kStream;                      // the MMA warp waits for the accumulator and wakes the epilogue warps (named barrier)
@@ -270,7 +278,7 @@ struct Cfg {
 // many stages as tensor memory has columns for (accumulator + 64 per stage <= 512).
 template <int NT, bool PAIR>
 struct ABStages {
-    static constexpr int value = !PAIR ? Cfg<NT>::kABStages : (Cfg<NT>::kDCols + 64 * 5 <= 512 ? 5 : 4);
+    static constexpr int value = !PAIR ? Cfg<NT, false>::kABStages : (Cfg<NT, true>::kDCols + 64 * 5 <= 512 ? 5 : 4);
 };
 
 struct Barriers {
@@ -303,12 +311,14 @@ struct TensorMaps {
 // tile is 256 weight columns x NT rows, each CTA dequantises its own 128 columns and loads only half of the rows of
 // the activation tile, which halves the L2 -> shared-memory traffic that bounds the many-row shapes.
 template <int BITS, bool SPARSE, int NT, bool PAIR>
-__global__ void __launch_bounds__(Cfg<NT>::kThreads, Cfg<NT>::kMinBlocks)
+__global__ void __launch_bounds__(Cfg<NT, PAIR>::kThreads, Cfg<NT, PAIR>::kMinBlocks)
 umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
     using F = UFormat<BITS, SPARSE>;
     using WS = WStage<F>;
-    using C = Cfg<NT>;
+    using C = Cfg<NT, PAIR>;
     static_assert(!PAIR || (NT >= 128 && !C::kEpiHandoff), "CTA pairs are for the many-row shapes");
+    static_assert((2 * C::kWStages) % C::kWG == 0, "every second use of a weight stage must be by the same warpgroup");
+    static_assert(ABStages<NT, PAIR>::value >= C::kWG, "fewer A stages than warpgroups: a parity wait could see the phase before last");
     constexpr int kBHalfBytes = (PAIR ? NT / 2 : NT) * 128;        // one 64-k activation sub-tile held by this CTA
     constexpr int kBStageBytes = 2 * kBHalfBytes;
     // single CTAs at NT = 256 have no shared memory left for a second transposition tile: the second epilogue group idles
@@ -833,6 +843,11 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
                     const uint32_t si = si0 + (uint32_t)(u - u0);
                     const uint32_t ws = si % C::kWStages, wph = (si / C::kWStages) & 1u;     // constants: multiply-shift, no division
                     if (warp == 0) TRACE(2, (int)si, 0);
+                    if (C::kWGuard && !ptx::mbar_wait(ptx::smem_u32(&bars.w_empty[ws]), wph ^ 1u)) {   // see Cfg::kWStages
+                        if (lane == 0) atomicExch(p.status, 35);
+                        ok = false;
+                        break;
+                    }
                     if (!ptx::mbar_wait(ptx::smem_u32(&bars.w_full[ws]), wph)) {
                         if (lane == 0) atomicExch(p.status, 31);
                         ok = false;
@@ -1013,7 +1028,7 @@ int launch_nt(const UmmaParams& p_in, const __half* x, int n_groups, cudaStream_
     UmmaParams p = p_in;
     p.kparts = 1;
     using F = UFormat<BITS, SPARSE>;
-    using C = Cfg<NT>;
+    using C = Cfg<NT, PAIR>;
     constexpr int kBStageBytes = 2 * (PAIR ? NT / 2 : NT) * 128;
     TensorMaps tm;
     const uint64_t R = SPARSE ? (uint64_t)p.N / 16 : (uint64_t)p.N * BITS / 32;
