@@ -5,7 +5,8 @@
 
 One step = one operator call (`quant_matmul`) over one batch of synthetic activations.  The default
 workload is the int4 dense matmul at M = 2048 on the 5120 x 20480 matrix (group 128), the configuration
-the headline TFLOP/s figure is quoted on; `--workload int4_matvec_16384` is the matvec half of the metric.
+the headline TFLOP/s figure is quoted on; the default run also times the matvec half of the metric (int4,
+16384 x 16384, one activation row) with the same protocol and prints it under the key `matvec` of the same line.
 With --gpus N (launched under torch.distributed.run, one rank per GPU) the weight matrix is column-
 sharded along S over the ranks (every rank computes its own S/N columns of the same product: total work
 fixed, "strong" scaling); there is no collective inside the timed region.
@@ -18,6 +19,10 @@ Prints ONE JSON line on rank 0.  Keys beyond the basic contract:
   e2e           the same metric through the drop-in torch extension module with HOST buffers: per step
                 one pinned host->device copy of the activations and one device->host copy of the result
   clocks        SM clock samples taken with nvidia-smi during the timed region
+  parity        the outputs the timed steps left behind, checked on sampled output columns against the CPU oracle
+                after the timed region (every rank checks its own shard; rank 0 prints the worst)
+  torch_fp16    torch's fp16 `x @ W16` (cuBLAS) on the dequantised matrix, the reference script's own comparator
+                (kernel_test.py:248-249, 296), timed on the same GPU with the same events
 `--impl reference` times the reference's algorithm on the host CPU (the reference itself is CUDA-only and
 has no CPU implementation; its test script's torch dequantise-and-matmul comparator is what runs).
 """
@@ -53,12 +58,12 @@ WORKLOADS = {
 # the ranks with an all-gather of every matrix's outputs; "m" = activation rows
 STACK_WORKLOADS = {f"stack13b_m{m}": m for m in (1, 16, 128, 2048)}
 DEFAULT_WORKLOAD = "int4_matmul_m2048_5120x20480"
+MATVEC_WORKLOAD = "int4_matvec_16384"            # the other half of the metric: timed by the default run as well
 
-# DRAM bytes per launch of the dominant kernel from ncu captures (dram__bytes_read.sum + dram__bytes_write.sum);
-# the summaries are under profiles/.  None = not captured for that workload.
+# DRAM bytes per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of
+# the unsharded workload), with the first 12 hex digits of the SHA-256 of csrc/umma_kernel.cu as it was when the
+# capture was made: the figure is printed only while the kernel source still is that file, else `traffic` is null.
 NCU_TRAFFIC_BYTES = {
-    "int4_matmul_m2048_5120x20480": 298.9e6,    # profiles/umma_kernel_int4_matmul_m2048_5120x20480.md
-    "int4_matvec_16384": 146.4e6,               # profiles/umma_kernel_int4_matvec_16384.md
 }
 
 L2_BYTES = 126 * 1024 * 1024
@@ -133,8 +138,30 @@ class ClockSampler:
 
 
 def cpu_problem(w, seed=0):
-    from oracle import reference_oracle as oracle    # the CPU legs are the one place the benchmark runs oracle/
-    return oracle.make_problem(w["bits"], w["n"], w["s"], w["m"], w["g"], sparse=w["sparse"], seed=seed)
+    from oracle import cpu_baseline                  # the CPU legs and the parity check are where the benchmark runs oracle/
+    return cpu_baseline.synthetic_unpacked(w["bits"], w["n"], w["s"], w["m"], w["g"], w["sparse"], seed)
+
+
+def kernel_source_tag():
+    import hashlib
+    path = os.path.join(ROOT, "int4matmul_kernels_b200", "csrc", "umma_kernel.cu")
+    with open(path, "rb") as f:
+        return hashlib.sha256(f.read()).hexdigest()[:12]
+
+
+def ncu_traffic(name, world):
+    rec = NCU_TRAFFIC_BYTES.get(name)
+    if rec is None or world != 1:
+        return None
+    return rec[0] if rec[1] == kernel_source_tag() else None
+
+
+L2_RULE = "weights rotate over enough copies that consecutive steps miss L2 (copies x bytes per step > 2 x L2)"
+
+
+def config_of(name, w):
+    """Identical in both arms."""
+    return dict(workload=name, **{k: w[k] for k in ("bits", "n", "s", "m", "g", "sparse")}, l2=L2_RULE)
 
 
 def cpu_reference_seconds(w, problem, rows, cores):
@@ -151,11 +178,14 @@ def reference_cuda_seconds(w, layer, x, torch):
     tensors, beside the product: a baseline leg like the CPU one, never part of the product path.  None if absent."""
     import glob
     import importlib.util
-    cand = glob.glob(os.path.join(ROOT, "oracle", "_ref", "int4matmul_ref*.so"))
+    # the matvec kernels are timed from the module whose matvec translation unit was compiled at default optimisation
+    # (oracle/build_reference.py); it has no dense int3 matvec
+    modname = "int4matmul_ref_timing" if w["m"] == 1 else "int4matmul_ref"
+    cand = glob.glob(os.path.join(ROOT, "oracle", "_ref", modname + ".*.so"))
     if not cand or (w["bits"] == 3 and w["m"] == 1):
         return None
     try:
-        spec = importlib.util.spec_from_file_location("int4matmul_ref", cand[0])
+        spec = importlib.util.spec_from_file_location(modname, cand[0])
         ref = importlib.util.module_from_spec(spec)
         spec.loader.exec_module(ref)
         out = torch.zeros((1, w["m"], layer["matrix"].shape[1]), dtype=torch.float16, device=x.device)
@@ -179,9 +209,10 @@ def reference_cuda_seconds(w, layer, x, torch):
         np_ = os.path.join(ROOT, "oracle", "_ref", "BUILD_NOTES.txt")
         if os.path.exists(np_):
             notes = open(np_).read().strip()
-        return dict(value=units_per_step(w, kind) / sec, unit=metric_of(w)[1], us_per_call=sec * 1e6,
+        return dict(value=units_per_step(w, kind) / sec, unit=metric_of(w)[1], us_per_call=sec * 1e6, module=modname,
                     what="reference quant_matmul (its WMMA / CUDA-core kernels compiled for sm_100), same tensors, "
-                         "its own stream and temporaries, 10 calls", build_notes=notes)
+                         "its own stream and temporaries (the matvec route: 3 torch kernels and 2 allocations per call), 10 calls",
+                    build_notes=notes)
     except Exception as e:
         return dict(unavailable=f"{type(e).__name__}: {e}")
 
@@ -198,12 +229,9 @@ def units_per_step(w, kind, s_cols=None):
     return algorithmic_bytes(w, s_cols) / 1e9 if kind == "hbm" else algorithmic_flops(w, s_cols) / 1e12
 
 
-def run_reference(args, w, name):
-    """--impl reference: the reference's algorithm on this host's CPU cores (see module docstring)."""
+def reference_line(args, w, name):
+    """The reference's algorithm on this host's CPU cores for one workload: a dict in the bench line's format."""
     import torch
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
-        return
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
     metric, unit, kind = metric_of(w)
@@ -218,12 +246,21 @@ def run_reference(args, w, name):
     value = units_per_step(w, kind) / sec
     sample = (f"per step: full {w['n']}x{w['s']} dequantise timed whole, matmul timed on {rows} of {w['m']} rows "
               "and scaled to all rows")
-    line = dict(metric=metric, value=value, unit=unit, n_gpus=args.gpus, steps=args.steps, warmup=args.warmup,
+    return dict(metric=metric, value=value, unit=unit, n_gpus=args.gpus, steps=args.steps, warmup=args.warmup,
                 ms_per_step=sec * 1e3, higher_is_better=True, scaling="strong", vs_baseline=None,
-                dtype="f16", data="synthetic", impl="reference",
-                config=dict(workload=name, **{k: w[k] for k in ("bits", "n", "s", "m", "g", "sparse")}),
-                cpu_baseline=dict(value=value, unit=unit, cores=cores, kind="port", sample=sample),
+                dtype="f16", data="synthetic", impl="reference", config=config_of(name, w),
+                cpu_baseline=dict(value=value, unit=unit, cores=cores, kind="port", sample=sample,
+                                  spread=[units_per_step(w, kind) / max(times), units_per_step(w, kind) / min(times)]),
                 e2e=dict(value=value, unit=unit, h2d_bytes_per_step=0, d2h_bytes_per_step=0))
+
+
+def run_reference(args, w, name):
+    """--impl reference: the reference's algorithm on this host's CPU cores (see module docstring)."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    line = reference_line(args, w, name)
+    if name == DEFAULT_WORKLOAD and not args.no_matvec:
+        line["matvec"] = reference_line(args, WORKLOADS[MATVEC_WORKLOAD], MATVEC_WORKLOAD)
     print(json.dumps(line))
 
 
@@ -394,45 +431,80 @@ def run_stack(args):
         dist.destroy_process_group()
 
 
-def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS) + sorted(STACK_WORKLOADS))
-    ap.add_argument("--layers", type=int, default=40, help="layers of the stack workloads")
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--path", type=int, default=0, help="0 auto, 1 streaming kernel, 2 tcgen05 kernel")
-    ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--no-graph", action="store_true", help="launch the timed steps directly instead of as one CUDA graph")
-    args = ap.parse_args()
-    args.warmup = max(args.warmup, 0)
-    if args.workload in STACK_WORKLOADS:
-        run_stack(args)
-        return
-    w = WORKLOADS[args.workload]
-    if args.impl == "reference":
-        run_reference(args, w, args.workload)
-        return
+def sample_columns(s, count, seed):
+    """Output columns to check: tile edges of both tile widths, the shard's edges, and random columns."""
+    import numpy as np
+    rng = np.random.default_rng(seed)
+    edges = [0, 1, 127, 128, 255, 256, s // 2 - 1, s // 2, s - 257, s - 129, s - 128, s - 1]
+    cols = set(c for c in edges if 0 <= c < s)
+    cols.update(int(c) for c in rng.integers(0, s, size=count))
+    return np.array(sorted(cols))
 
+
+def check_outputs(w, chain, x_cpu, out, cols, accumulate_from_zero):
+    """One output buffer against the CPU oracle on the columns `cols` (reference semantics: fp16 weights as the
+    reference rebuilds them, fp32 accumulation, one rounding).  `chain` = the weight copies multiplied into the
+    buffer, in order: one for the overwriting matmul route; for the matvec route, which adds into the buffer,
+    every launch since the buffer was zeroed (each adds to the rounded result of the one before).  Returns
+    (elements checked, out of tolerance, worst ulp distance, fraction bit-identical).  Tolerance as in the tests:
+    1 fp16 ulp, or 2^-13 of sum |x . W16|."""
+    import numpy as np
     import torch
-    import torch.distributed as dist
-    from int4matmul_kernels_b200 import capi, ops, packing
-    import int4matmul_kernels_b200 as pkg
+    from oracle import reference_oracle as oracle            # checker only, after the timed region
+    ci = torch.as_tensor(cols, device=chain[0]["matrix"].device)
+    sub = lambda t: t.index_select(1, ci).cpu().numpy() if t is not None else None
+    want = np.zeros((1, w["m"], len(cols)), np.float16) if accumulate_from_zero else None
+    bound = 0.0
+    for layer in chain:
+        want, b = oracle.expected_columns(w["bits"], sub(layer["matrix"]), sub(layer["mask"]), sub(layer["scales"]),
+                                          sub(layer["zeros"]), w["g"], x_cpu, np.arange(len(cols)), want)
+        bound = bound + b
+        if not accumulate_from_zero:
+            break
+    got = out.index_select(out.dim() - 1, ci.to(out.device)).cpu().numpy().reshape(want.shape)
+    ulp = oracle.fp16_ulp_distance(got, want)
+    diff = np.abs(got.astype(np.float32) - want.astype(np.float32))
+    ok = (ulp <= 1) | (diff <= 2.0 ** -13 * bound)
+    return int(ok.size), int((~ok).sum()), int(ulp.max()), float((ulp == 0).mean())
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device: the operator has no CPU path")
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    if world > 1:
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=dev)
-    capi.load()                                   # fails loudly if the CUDA library is missing
-    ext = pkg.load_extension()
+
+def torch_fp16_leg(w, layer, x, torch, steps):
+    """torch's own fp16 matmul on the dequantised weights, as the reference script times it (kernel_test.py:248-249,
+    296): a library comparator beside the product, never part of its path.  Dense formats only."""
+    if w["sparse"]:
+        return None
+    from int4matmul_kernels_b200 import packing, quantize
+    try:
+        q = packing.unpack_dense(w["bits"], layer["matrix"])
+        w16 = quantize.dequantize(q, layer["scales"], layer["zeros"], w["g"])
+        del q
+        x2 = x.view(w["m"], w["n"])
+        for _ in range(3):
+            y = x2 @ w16
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        iters = max(steps, 10)
+        e0.record()
+        for _ in range(iters):
+            y = x2 @ w16
+        e1.record()
+        torch.cuda.synchronize()
+        sec = e0.elapsed_time(e1) / iters / 1e3
+        del w16, y
+        kind = metric_of(w)[2]
+        return dict(us_per_call=sec * 1e6, value=units_per_step(w, kind, layer["matrix"].shape[1]) / sec, unit=metric_of(w)[1],
+                    what=f"torch fp16 x @ W16 (cuBLAS) on the already dequantised {w['n']}x{layer['matrix'].shape[1]} matrix, {iters} back-to-back calls; "
+                         "for few rows it reads 2 bytes per weight where the packed formats read bits/8")
+    except Exception as e:                                # a comparator: its failure is reported, not fatal
+        return dict(unavailable=f"{type(e).__name__}: {e}")
+
+
+def run_workload(args, name, w, ctx):
+    """Times one workload on this rank's column shard; returns the line's dict on rank 0 (None elsewhere)."""
+    torch, dist, dev = ctx["torch"], ctx["dist"], ctx["dev"]
+    world, rank, local_rank, ext = ctx["world"], ctx["rank"], ctx["local_rank"], ctx["ext"]
+    from int4matmul_kernels_b200 import capi, ops, packing
+    lib = capi.load()
 
     metric, unit, kind = metric_of(w)
     s_local = w["s"] // world
@@ -451,19 +523,24 @@ def main():
     gen = torch.Generator().manual_seed(1234)
     x_host = torch.randn((1, w["m"], w["n"]), generator=gen).to(torch.float16).pin_memory()
     x = x_host.to(dev)
-    outs = [torch.zeros((1, w["m"], s_local), dtype=torch.float16, device=dev) for _ in range(min(copies, 4))]
+    matvec = w["m"] == 1                                     # the matvec route adds into outs
+    # matvec: one output buffer per step, all zeroed by ONE fill at the start of every run of K steps, so that what a
+    # buffer holds afterwards is a known chain of accumulations without a fill kernel between the timed launches
+    n_out = min(args.steps, 64) if matvec else min(copies, 4)
+    out_all = torch.zeros((n_out, 1, w["m"], s_local), dtype=torch.float16, device=dev)
+    outs = [out_all[j] for j in range(n_out)]
 
     def step(i):
         L = layers[i % copies]
-        ops.quant_matmul(w["bits"], outs[i % len(outs)], L["matrix"], x, L["scales"], L["zeros"], w["g"], L["mask"],
-                         path=args.path)
+        if matvec and i == 0:
+            out_all.zero_()
+        ops.quant_matmul(w["bits"], outs[i % n_out], L["matrix"], x, L["scales"], L["zeros"], w["g"], L["mask"], path=args.path)
 
     use_umma = args.path != 1                       # automatic = the tcgen05 kernel for every row count
-    launches_per_step = 1 if use_umma else -(-w["m"] // 32)
-
     for i in range(max(args.warmup, 3)):
         step(i)
     torch.cuda.synchronize()
+    shape = lib.i4mm_last_launch_shape()
 
     graph = None
     if not args.no_graph:
@@ -474,11 +551,11 @@ def main():
                 step(0)                                   # allocates this stream's scratch outside the capture
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
-            n0 = capi.load().i4mm_launch_count()
+            n0 = lib.i4mm_launch_count()
             with torch.cuda.graph(graph, stream=side):
                 for i in range(args.steps):
                     step(i)
-            k_launches = capi.load().i4mm_launch_count() - n0      # kernels of ours in the K captured steps
+            k_launches = lib.i4mm_launch_count() - n0      # kernels of ours in the K captured steps
             graph.replay()
             torch.cuda.synchronize()
         except Exception as e:                            # capture is an optimisation of the harness only
@@ -491,10 +568,10 @@ def main():
         torch.cuda.synchronize()
 
     if graph is None:
-        n0 = capi.load().i4mm_launch_count()
+        n0 = lib.i4mm_launch_count()
         for i in range(args.steps):
             step(i)
-        k_launches = capi.load().i4mm_launch_count() - n0
+        k_launches = lib.i4mm_launch_count() - n0
 
     def run_steps():
         if graph is not None:
@@ -528,42 +605,83 @@ def main():
     ms_step = ms_total / args.steps
     value = units_per_step(w, kind) / (ms_step / 1e3)          # whole job: all shards together per step
 
+    # ---- parity of what the timed steps left in the output buffers (outside the timed region) ----
+    x_cpu = x_host.numpy()
+    writers = {}                                             # output buffer -> the weight copies written into it, in order
+    for i in range(args.steps):
+        writers.setdefault(i % n_out, []).append(i % copies)
+    checked = bad = 0
+    worst_ulp, exact = 0, 1.0
+    n_cols = 0
+    for j, chain in sorted(writers.items())[:8]:
+        cols = sample_columns(s_local, 64, 17 * j + rank)
+        n, b, u, fe = check_outputs(w, [layers[li] for li in (chain if matvec else chain[-1:])], x_cpu, outs[j], cols, matvec)
+        checked, bad, worst_ulp, exact, n_cols = checked + n, bad + b, max(worst_ulp, u), min(exact, fe), n_cols + len(cols)
+    status_ok = lib.i4mm_device_status(ops.workspace(dev, torch.cuda.current_stream()).data_ptr(), torch.cuda.current_stream().cuda_stream) == capi.OK
+
     # ---- roofline of the dominant kernel (this rank's launch) ----
     peaks = measured_peaks()
-    us_launch = ms_step * 1e3 / launches_per_step
+    us_launch = ms_step * 1e3
+    gbs = algorithmic_bytes(w, s_local) / 1e9 / (ms_step / 1e3)
+    tfs = algorithmic_flops(w, s_local) / 1e12 / (ms_step / 1e3)
     if kind == "hbm":
-        achieved = algorithmic_bytes(w, s_local) / 1e9 / (ms_step / 1e3)
-        peak, runit = peaks["hbm"], "GB/s"
+        achieved, peak, runit = gbs, peaks["hbm"], "GB/s"
     else:
-        achieved = algorithmic_flops(w, s_local) / 1e12 / (ms_step / 1e3)
-        peak, runit = peaks["tf_burst"], "TFLOP/s"
+        achieved, peak, runit = tfs, peaks["tf_burst"], "TFLOP/s"
     roofline = dict(bound=kind, achieved=achieved, peak=peak, unit=runit, frac=achieved / peak,
-                    traffic=NCU_TRAFFIC_BYTES.get(args.workload) if world == 1 else None,   # captured for the unsharded launch only
-                    peak_source=peaks["source"],
+                    traffic=ncu_traffic(name, world), peak_source=peaks["source"],
                     us_per_launch=us_launch, kernel="umma_kernel (tcgen05)" if use_umma else "stream_kernel (mma.sync)",
-                    frac_of_nominal=achieved / (8000.0 if kind == "hbm" else 2250.0))
+                    launch_shape=shape, frac_of_nominal=achieved / (8000.0 if kind == "hbm" else 2250.0),
+                    frac_of_sustained_bf16=(tfs / peaks["tf_sustained"]) if kind == "tensor" else None)
+    if 16 <= w["m"] <= 256:
+        # near the ridge (arithmetic intensity ~ the machine balance): report against both roofs
+        roofline["both_roofs"] = dict(hbm=dict(achieved=gbs, peak=peaks["hbm"], frac=gbs / peaks["hbm"], unit="GB/s"),
+                                      tensor=dict(achieved=tfs, peak=peaks["tf_burst"], frac=tfs / peaks["tf_burst"], unit="TFLOP/s"))
 
-    # ---- end to end through the drop-in module, host buffers ----
+    # ---- end to end through the drop-in module, host buffers: H2D(i+1) | kernel(i) | D2H(i-1) on three streams ----
     e2e = None
     if not args.no_e2e:
-        out_host = torch.empty((1, w["m"], s_local), dtype=torch.float16).pin_memory()
-        x_dev = torch.empty_like(x)
-        o_dev = torch.zeros((1, w["m"], s_local), dtype=torch.float16, device=dev)
+        s_in, s_k, s_out = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
+        x_dev = [torch.empty_like(x) for _ in range(2)]
+        o_dev = [torch.zeros((1, w["m"], s_local), dtype=torch.float16, device=dev) for _ in range(2)]
+        out_host = [torch.empty((1, w["m"], s_local), dtype=torch.float16).pin_memory() for _ in range(2)]
+        ev_in = [torch.cuda.Event() for _ in range(2)]
+        ev_k = [torch.cuda.Event() for _ in range(2)]
+        ev_out = [torch.cuda.Event() for _ in range(2)]
 
         def e2e_step(i):
+            b = i % 2
             L = layers[i % copies]
-            x_dev.copy_(x_host, non_blocking=True)
-            if w["m"] == 1:
-                o_dev.zero_()                              # the matvec route adds into outs
-            ext.quant_matmul(w["bits"], o_dev, L["matrix"], x_dev, L["scales"], L["zeros"], w["g"], L["mask"])
-            out_host.copy_(o_dev, non_blocking=True)
+            with torch.cuda.stream(s_in):
+                s_in.wait_event(ev_k[b])                   # the kernel that last read this input buffer
+                x_dev[b].copy_(x_host, non_blocking=True)
+                ev_in[b].record(s_in)
+            with torch.cuda.stream(s_k):
+                s_k.wait_event(ev_in[b])
+                s_k.wait_event(ev_out[b])                  # the copy that last read this output buffer
+                if matvec:
+                    o_dev[b].zero_()
+                ext.quant_matmul(w["bits"], o_dev[b], L["matrix"], x_dev[b], L["scales"], L["zeros"], w["g"], L["mask"])
+                ev_k[b].record(s_k)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(ev_k[b])
+                out_host[b].copy_(o_dev[b], non_blocking=True)
+                ev_out[b].record(s_out)
 
-        for i in range(3):
-            e2e_step(i)
+        cur = torch.cuda.current_stream()
+
+        def e2e_run(n):
+            for st in (s_in, s_k, s_out):
+                st.wait_stream(cur)
+            for i in range(n):
+                e2e_step(i)
+            for st in (s_in, s_k, s_out):
+                cur.wait_stream(st)
+
+        e2e_run(3)
         barrier()
         e0.record()
-        for i in range(args.steps):
-            e2e_step(i)
+        e2e_run(args.steps)
         e1.record()
         barrier()
         ms_e2e = e0.elapsed_time(e1)
@@ -571,12 +689,31 @@ def main():
             t = torch.tensor([ms_e2e], device=dev)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             ms_e2e = float(t.item())
+        # the host copy of the last step's result is checked as well
+        last = args.steps - 1
+        cols = sample_columns(s_local, 48, 99 + rank)
+        n, b, u, fe = check_outputs(w, [layers[last % copies]], x_cpu, out_host[last % 2].to(dev), cols, matvec)
+        checked, bad, worst_ulp, exact, n_cols = checked + n, bad + b, max(worst_ulp, u), min(exact, fe), n_cols + len(cols)
         e2e = dict(value=units_per_step(w, kind) / (ms_e2e / args.steps / 1e3), unit=unit,
-                   h2d_bytes_per_step=x_host.numel() * 2, d2h_bytes_per_step=out_host.numel() * 2,
-                   ms_per_step=ms_e2e / args.steps)
+                   h2d_bytes_per_step=x_host.numel() * 2, d2h_bytes_per_step=out_host[0].numel() * 2,
+                   ms_per_step=ms_e2e / args.steps,
+                   how="int4matmul.quant_matmul on pinned host buffers; input copy, kernel and result copy of consecutive steps "
+                       "overlap on three streams (double-buffered)")
 
-    # ---- CPU baseline on a bounded sample (rank 0, one GPU only) ----
-    cpu = None
+    if world > 1:
+        t = torch.tensor([float(checked), float(bad), float(n_cols)], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        t2 = torch.tensor([float(worst_ulp), -exact, 0.0 if status_ok else 1.0], device=dev)
+        dist.all_reduce(t2, op=dist.ReduceOp.MAX)
+        checked, bad, n_cols = int(t[0].item()), int(t[1].item()), int(t[2].item())
+        worst_ulp, exact, status_ok = int(t2[0].item()), -float(t2[1].item()), t2[2].item() == 0.0
+    parity = dict(checked=True, ok=(bad == 0 and status_ok), elements=checked, out_of_tolerance=bad, max_ulp=worst_ulp,
+                  frac_bit_identical=exact, cols=n_cols, ranks=world, device_status_ok=status_ok,
+                  against="CPU oracle (reference semantics) on sampled output columns of the buffers the timed steps wrote",
+                  tolerance="1 fp16 ulp or 2^-13 * sum|x.W16|")
+
+    # ---- CPU baseline on a bounded sample; the reference's CUDA kernels and torch fp16 beside it (rank 0, one GPU) ----
+    cpu = ref_gpu = torch16 = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         cores = os.cpu_count() or 1
         torch.set_num_threads(cores)
@@ -585,24 +722,76 @@ def main():
         cpu_reference_seconds(w, p, rows, cores)
         reps = 3
         sec = min(cpu_reference_seconds(w, p, rows, cores) for _ in range(reps))
+        del p
         cpu = dict(value=units_per_step(w, kind) / sec, unit=unit, cores=cores, kind="port",
                    sample=(f"full {w['n']}x{w['s']} dequantise timed whole, matmul timed on {rows} of {w['m']} rows and "
                            f"scaled to all rows, best of {reps}"))
-
-    # ---- the reference's own CUDA kernels on this GPU, when the build made by oracle/build_reference.py is present ----
-    ref_gpu = None
-    if rank == 0 and world == 1 and not args.no_cpu_baseline:
         ref_gpu = reference_cuda_seconds(w, layers[0], x, torch)
+        torch16 = torch_fp16_leg(w, layers[0], x, torch, args.steps)
 
+    if rank != 0:
+        return None
+    return dict(metric=metric, value=value, unit=unit, n_gpus=world, steps=args.steps, warmup=max(args.warmup, 3),
+                ms_per_step=ms_step, higher_is_better=True, scaling="strong", vs_baseline=None,
+                dtype="f16", data="synthetic", config=config_of(name, w),
+                protocol=dict(sharding=f"S columns over {world} GPU(s)", weight_copies=copies,
+                              timed_as="one CUDA graph of the K steps" if graph is not None else "K direct launches",
+                              outputs=(f"{n_out} output buffers zeroed by one fill per K steps (the matvec route adds into them)"
+                                       if matvec else f"{n_out} output buffers, overwritten")),
+                roofline=roofline, parity=parity, cpu_baseline=cpu, reference_cuda=ref_gpu, torch_fp16=torch16, e2e=e2e,
+                clocks=clocks.summary(), gpu_launches=int(k_launches))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS) + sorted(STACK_WORKLOADS))
+    ap.add_argument("--layers", type=int, default=40, help="layers of the stack workloads")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--path", type=int, default=0, help="0 auto, 1 streaming kernel, 2 tcgen05 kernel, 3 tcgen05 with single CTAs")
+    ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU baseline and the comparator legs")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-matvec", action="store_true", help="default workload only: do not time the matvec half of the metric as well")
+    ap.add_argument("--no-graph", action="store_true", help="launch the timed steps directly instead of as one CUDA graph")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 0)
+    if args.workload in STACK_WORKLOADS:
+        run_stack(args)
+        return
+    w = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        run_reference(args, w, args.workload)
+        return
+
+    import torch
+    import torch.distributed as dist
+    from int4matmul_kernels_b200 import capi
+    import int4matmul_kernels_b200 as pkg
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the operator has no CPU path")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    capi.load()                                   # fails loudly if the CUDA library is missing
+    ctx = dict(torch=torch, dist=dist, dev=dev, world=world, rank=rank, local_rank=local_rank, ext=pkg.load_extension())
+
+    line = run_workload(args, args.workload, w, ctx)
+    if args.workload == DEFAULT_WORKLOAD and not args.no_matvec:
+        # the other half of the metric, same protocol, under one extra key of the same line
+        torch.cuda.empty_cache()
+        mv = run_workload(args, MATVEC_WORKLOAD, WORKLOADS[MATVEC_WORKLOAD], ctx)
+        if line is not None:
+            line["matvec"] = mv
+            line["gpu_launches_matvec"] = mv["gpu_launches"]
     if rank == 0:
-        line = dict(metric=metric, value=value, unit=unit, n_gpus=world, steps=args.steps, warmup=max(args.warmup, 3),
-                    ms_per_step=ms_step, higher_is_better=True, scaling="strong", vs_baseline=None,
-                    dtype="f16", data="synthetic",
-                    config=dict(workload=args.workload, **{k: w[k] for k in ("bits", "n", "s", "m", "g", "sparse")},
-                                sharding=f"S columns over {world} GPU(s)", l2="rotating %d weight copies (> 2x L2)" % copies,
-                                timed_as="one CUDA graph of the K steps" if graph is not None else "K direct launches"),
-                    roofline=roofline, cpu_baseline=cpu, reference_cuda=ref_gpu, e2e=e2e, clocks=clocks.summary(),
-                    gpu_launches=int(k_launches))
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()

@@ -52,6 +52,10 @@ int i4mm_version(void);
 /* Kernels this library has launched in this process so far, over all entry points (a multiply is one launch,
  * or two where it cuts K into parts and reduces them).  For accounting in benchmarks; no reference counterpart. */
 unsigned long long i4mm_launch_count(void);
+/* What the last i4mm_quant_matmul call of this host thread launched on the tcgen05 path: rows per tile (the MMA's N:
+ * 16, 32, 64, 128, 160, 192, 224 or 256) + 1000 if it ran as CTA pairs + 10000 * K parts; 0 after a call that took the
+ * streaming path.  For tests that must know which kernel instance they exercised; no reference counterpart. */
+int i4mm_last_launch_shape(void);
 
 /*
  * Bytes of device scratch the two multiply entries need.  The scratch holds the per-CTA partial tiles
@@ -78,6 +82,9 @@ size_t i4mm_workspace_bytes(void);
  *   0 = automatic (the tcgen05 kernel when the driver's tensor-map encoder is found), 1 = streaming (mma.sync,
  *   split-K over the whole GPU), 2 = tcgen05 / TMEM pipeline (128 rows or more run as CTA pairs, two SMs per
  *   MMA), 3 = tcgen05 with single CTAs only.
+ *   With path 2 or 3, `path | (T << 8)` also fixes the rows per tile (the MMA's N) to T in {16, 32, 64, 128, 160, 192,
+ *   224, 256} instead of choosing it by shape (T >= 128 with path 2 runs as CTA pairs; T <= 64 needs rows <= T):
+ *   for tests and tuning, results do not depend on it beyond fp32 summation order.
  */
 int i4mm_quant_matmul(int bits, int accumulate, int path,
                       void* out, const void* matrix, const void* mask /* NULL = dense */,
@@ -97,7 +104,7 @@ int i4mm_quant_matmul(int bits, int accumulate, int path,
  *   set-up   the first call on each device looks up the array's device address (cudaGetSymbolAddress) and
  *            configures the kernel; make that first call before any stream capture begins
  *   sharing  every call on a device uses the same array, which keeps the previous call's contents; the entry
- *            clears the counters it needs (two small memsets on `stream`) before launching.  Two calls that
+ *            clears the counters it needs (one small memset on `stream`) before launching.  Two calls that
  *            overlap on the GPU (different streams, or different host threads) race on it: serialise them.
  *   It calls no cudaMalloc, cudaFree or any allocating library routine.  Results are identical to
  *   i4mm_quant_matmul(path = 1) on the same inputs.
@@ -114,6 +121,9 @@ int i4mm_quant_matvec_static(int bits, int accumulate,
  * I4MM_ERR_TIMEOUT after clearing the word.  No counterpart in the reference, whose kernels have no waits.
  */
 int i4mm_device_status(void* workspace, void* stream);
+/* The same check for i4mm_quant_matvec_static, whose status word lives in the library's fixed scratch on the
+ * current device: waits for the stream, returns I4MM_OK or (after clearing the word) I4MM_ERR_TIMEOUT. */
+int i4mm_static_device_status(void* stream);
 
 /*
  * 16:32 packer.  Replaces sparse_int4_pack / PackMatrix (utils_kernel.cu:67-119, 19-64).

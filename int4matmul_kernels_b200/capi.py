@@ -7,9 +7,7 @@ from __future__ import annotations
 import ctypes
 import os
 
-# INT4MATMUL_B200_LIB points at an alternative build of the same library (e.g. one compiled with other tuning macros)
-_LIB_PATH = os.environ.get("INT4MATMUL_B200_LIB") or os.path.join(
-    os.path.dirname(os.path.abspath(__file__)), "lib", "libint4matmul_b200.so")
+_LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib", "libint4matmul_b200.so")
 _lib = None
 
 OK = 0
@@ -24,6 +22,7 @@ _SIGNATURES = {
     "i4mm_last_cuda_error": (ctypes.c_int, []),
     "i4mm_version": (ctypes.c_int, []),
     "i4mm_launch_count": (ctypes.c_ulonglong, []),
+    "i4mm_last_launch_shape": (ctypes.c_int, []),
     "i4mm_workspace_bytes": (ctypes.c_size_t, []),
     "i4mm_quant_matmul": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, ctypes.c_int,
                                          ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
@@ -36,6 +35,7 @@ _SIGNATURES = {
                                                 ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
                                                 ctypes.c_void_p]),
     "i4mm_device_status": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p]),
+    "i4mm_static_device_status": (ctypes.c_int, [ctypes.c_void_p]),
     "i4mm_row_norm": (ctypes.c_int, [ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
                                      ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
                                      ctypes.c_void_p]),

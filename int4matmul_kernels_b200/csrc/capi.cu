@@ -9,6 +9,10 @@
 namespace i4mm {
 static std::atomic<unsigned long long> g_launches{0};
 void count_launch(int n) { g_launches.fetch_add((unsigned long long)n); }
+static thread_local int g_last_cuda_error = 0;        // what i4mm_last_cuda_error returns; every entry point records here
+void record_cuda_error(int e) { g_last_cuda_error = e; }
+int umma_last_shape();
+void umma_clear_last_shape();
 cudaError_t stream_launch(int bits, bool sparse, StreamParams p, int total_rows, int ctas, cudaStream_t stream);
 cudaError_t sparse_pack_launch(void* wt_out, void* msk_out, const void* wt_in, const void* msk_in,
                                int S, int N, void* violations, cudaStream_t stream);
@@ -16,26 +20,21 @@ cudaError_t check_mask_launch(const void* mask, size_t count, void* violations, 
 cudaError_t rownorm_launch(int mode, void* y, const void* a, const void* b, const void* c, long long rows, int width,
                            long long sa, long long sb, long long sc, cudaStream_t stream);
 int umma_launch(int bits, bool sparse, const StreamParams& p, int total_rows, int n_groups, int group_size, int cta_pairs,
-                cudaStream_t stream, cudaError_t* cuda_err);
+                int force_nt, cudaStream_t stream, cudaError_t* cuda_err);
 bool umma_supported(int bits, bool sparse, int total_rows, int N, int S);
 }  // namespace i4mm
 
 namespace {
 
-thread_local int g_last_cuda_error = 0;
-
 constexpr size_t kCounterBytes = 256 * 1024;          // column-tile counters; the last 64 bytes hold the status word
 constexpr size_t kStatusOffset = kCounterBytes - 64;
-#ifndef I4MM_STREAM_MAXCTAS
-#define I4MM_STREAM_MAXCTAS (148 * 4)
-#endif
-constexpr int kMaxStreamCtas = I4MM_STREAM_MAXCTAS;   // upper bound on the CTAs of the streaming kernel (sizes the scratch)
-constexpr size_t kPartialBytes = (size_t)(148 * 4) * 2 * 32 * 128 * sizeof(float);
+constexpr int kMaxStreamCtas = 148 * 4;               // upper bound on the CTAs of the streaming kernel (sizes the scratch)
+constexpr size_t kPartialBytes = (size_t)kMaxStreamCtas * 2 * 32 * 128 * sizeof(float);
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 int fail_cuda(cudaError_t e) {
-    g_last_cuda_error = (int)e;
+    i4mm::record_cuda_error((int)e);
     return I4MM_ERR_LAUNCH;
 }
 
@@ -61,7 +60,9 @@ const char* i4mm_status_string(int status) {
     }
 }
 
-int i4mm_last_cuda_error(void) { return g_last_cuda_error; }
+int i4mm_last_cuda_error(void) { return i4mm::g_last_cuda_error; }
+
+int i4mm_last_launch_shape(void) { return i4mm::umma_last_shape(); }
 
 int i4mm_version(void) { return 100; }
 
@@ -88,7 +89,16 @@ int i4mm_quant_matmul(int bits, int accumulate, int path,
     if (!aligned16(out) || !aligned16(matrix) || !aligned16(x) || !aligned16(scales) || !aligned16(zeros) ||
         (mask && !aligned16(mask)))
         return I4MM_ERR_ALIGN;
+    // bits 8.. of `path`: rows per tile to use on the tcgen05 path instead of the choice by shape (tests, tuning)
+    const int force_nt = path >= 0 ? path >> 8 : 0;
+    if (path >= 0) path &= 0xFF;
     if (path < 0 || path > 3) return I4MM_ERR_SHAPE;
+    if (force_nt != 0) {
+        const bool known = force_nt == 16 || force_nt == 32 || force_nt == 64 || force_nt == 128 || force_nt == 160 ||
+                           force_nt == 192 || force_nt == 224 || force_nt == 256;
+        // the few-row tiles reduce split-K partial tiles of one row tile only
+        if (!known || path < 2 || (force_nt <= 64 && rows > force_nt)) return I4MM_ERR_SHAPE;
+    }
 
     i4mm::StreamParams p{};
     p.out = (__half*)out;
@@ -122,10 +132,11 @@ int i4mm_quant_matmul(int bits, int accumulate, int path,
     }
     if (use_umma) {
         cudaError_t ce = cudaSuccess;
-        const int rc = i4mm::umma_launch(bits, sparse, p, (int)rows, (int)n_groups, (int)(group_size < 0 ? -1 : group_size), path == 3 ? 1 : 0, st, &ce);
+        const int rc = i4mm::umma_launch(bits, sparse, p, (int)rows, (int)n_groups, (int)(group_size < 0 ? -1 : group_size), path == 3 ? 1 : 0, force_nt, st, &ce);
         if (rc == I4MM_ERR_LAUNCH) return fail_cuda(ce);
         return rc;
     }
+    i4mm::umma_clear_last_shape();
     const cudaError_t e = i4mm::stream_launch(bits, sparse, p, (int)rows, kMaxStreamCtas, st);
     if (e != cudaSuccess) return fail_cuda(e);
     return I4MM_OK;
@@ -162,7 +173,8 @@ int i4mm_row_norm(int mode, void* y, const void* a, const void* b, const void* c
 
 int i4mm_sparse_pack(void* wt_out, void* msk_out, const void* wt_in, const void* msk_in,
                      int64_t S, int64_t N, void* violations, void* stream) {
-    if (S < 0 || N < 0 || N % 32 != 0 || N > (1 << 30) || S > (1 << 30)) return I4MM_ERR_SHAPE;   // utils_kernel.cu:101
+    // utils_kernel.cu:101; S is walked by the grid's y dimension in steps of 32 columns (at most 65535 of them)
+    if (S < 0 || N < 0 || N % 32 != 0 || N > (1 << 30) || S > 65535 * 32) return I4MM_ERR_SHAPE;
     if (S == 0 || N == 0) return I4MM_OK;
     if (!wt_out || !msk_out || !wt_in || !msk_in) return I4MM_ERR_NULL;
     if (!aligned16(wt_in) || !aligned16(msk_in) || !aligned16(wt_out) || !aligned16(msk_out)) return I4MM_ERR_ALIGN;

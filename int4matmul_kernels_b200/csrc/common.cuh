@@ -94,5 +94,7 @@ struct StreamParams {
 
 // Counts kernel launches of this library in this process (read through i4mm_launch_count); defined in capi.cu.
 void count_launch(int n = 1);
+// Stores the cudaError_t that i4mm_last_cuda_error() reports for the calling host thread; defined in capi.cu.
+void record_cuda_error(int e);
 
 }  // namespace i4mm

@@ -44,8 +44,6 @@ cudaError_t static_scratch_address(unsigned char** out) {
     return cudaSuccess;
 }
 
-thread_local int g_static_cuda_error = 0;
-
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 }  // namespace
@@ -71,7 +69,7 @@ extern "C" int i4mm_quant_matvec_static(int bits, int accumulate, void* out, con
 
     unsigned char* scratch = nullptr;
     cudaError_t e = static_scratch_address(&scratch);
-    if (e != cudaSuccess) { g_static_cuda_error = (int)e; return I4MM_ERR_LAUNCH; }
+    if (e != cudaSuccess) { i4mm::record_cuda_error((int)e); return I4MM_ERR_LAUNCH; }
 
     i4mm::StreamParams p{};
     p.out = (__half*)out;
@@ -92,13 +90,25 @@ extern "C" int i4mm_quant_matvec_static(int bits, int accumulate, void* out, con
     p.status = reinterpret_cast<int*>(scratch + kCountersBytes);
     p.partials = reinterpret_cast<float*>(scratch + kCountersBytes + kStatusBytes);
 
-    // The array keeps whatever the last call left.  The arrival counters and the status word must start at
-    // zero (a call that was cut short could have left them otherwise); the partial sums are overwritten before
-    // they are read.
+    // The array keeps whatever the last call left.  The arrival counters must start at zero (a call that was cut
+    // short could have left them otherwise); the partial sums are overwritten before they are read.  The status
+    // word is left alone: a give-up recorded by an earlier call stays visible until i4mm_static_device_status reads it.
     cudaStream_t st = (cudaStream_t)stream;
     e = cudaMemsetAsync(scratch, 0, (size_t)p.CT * sizeof(unsigned int), st);
-    if (e == cudaSuccess) e = cudaMemsetAsync(scratch + kCountersBytes, 0, kStatusBytes, st);
     if (e == cudaSuccess) e = i4mm::stream_launch(bits, sparse, p, (int)rows, kStaticCtas, st);
-    if (e != cudaSuccess) { g_static_cuda_error = (int)e; return I4MM_ERR_LAUNCH; }
+    if (e != cudaSuccess) { i4mm::record_cuda_error((int)e); return I4MM_ERR_LAUNCH; }
     return I4MM_OK;
+}
+
+// The status word of the fixed scratch: read (and cleared) the same way i4mm_device_status reads a workspace's.
+extern "C" int i4mm_static_device_status(void* stream) {
+    unsigned char* scratch = nullptr;
+    cudaError_t e = static_scratch_address(&scratch);
+    int status = 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (e == cudaSuccess) e = cudaMemcpyAsync(&status, scratch + kCountersBytes, sizeof(int), cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    if (e == cudaSuccess && status != 0) e = cudaMemsetAsync(scratch + kCountersBytes, 0, kStatusBytes, st);
+    if (e != cudaSuccess) { i4mm::record_cuda_error((int)e); return I4MM_ERR_LAUNCH; }
+    return status == 0 ? I4MM_OK : I4MM_ERR_TIMEOUT;
 }

@@ -15,6 +15,8 @@
 //   * the (column tile, k-block) space is cut into equal contiguous ranges, one per CTA, and ranges that
 //     split a column tile are summed through fp32 scratch in a fixed order by the last CTA to arrive
 //     (no atomics on data, bit-reproducible, no second launch).
+#include <atomic>
+
 #include "common.cuh"
 #include "ptx.cuh"
 
@@ -497,18 +499,13 @@ __device__ __forceinline__ int range_owner(long long T, long long G, long long t
     return (int)(((t + 1) * G + T - 1) / T - 1);
 }
 
-#ifndef I4MM_STREAM_STAGES
-#define I4MM_STREAM_STAGES 4
-#endif
-#ifndef I4MM_STREAM_MINBLOCKS
-#define I4MM_STREAM_MINBLOCKS 3
-#endif
-constexpr int kStages = I4MM_STREAM_STAGES;
+constexpr int kStages = 4;              // shared-memory ring stages
+constexpr int kMinBlocksOneRow = 3;     // CTAs per SM the one-m-tile kernel is compiled for
 constexpr int kConsumerWarps = 4;
 constexpr int kStreamThreads = (kConsumerWarps + 1) * 32;
 
 template <int BITS, bool SPARSE, int MT>
-__global__ void __launch_bounds__(kStreamThreads, (MT == 1 ? I4MM_STREAM_MINBLOCKS : MT == 2 ? 2 : 1))
+__global__ void __launch_bounds__(kStreamThreads, (MT == 1 ? kMinBlocksOneRow : MT == 2 ? 2 : 1))
 stream_kernel(const StreamParams p) {
     using F = Format<BITS, SPARSE>;
     using SL = StageLayout<F, MT>;
@@ -562,7 +559,9 @@ stream_kernel(const StreamParams p) {
 
     long long tile = t_lo;
     bool first_segment = true;
-    while (tile < t_hi && !failed) {
+    // A warp whose bounded wait gave up keeps walking its tiles without waiting or computing, so that it still
+    // arrives at every named barrier and ring barrier the other warps count on (results are void: the status says so).
+    while (tile < t_hi) {
         const int ct = (int)(tile / p.KB);
         const int kb0 = (int)(tile - (long long)ct * p.KB);
         const int kb1 = (int)min((long long)p.KB, kb0 + (t_hi - tile));
@@ -577,18 +576,15 @@ stream_kernel(const StreamParams p) {
                 for (int i = 0; i < 4; ++i) acc[mt][cp][i] = 0.f;
 
         for (int kb = kb0; kb < kb1; ++kb) {
-            if (!ptx::mbar_wait(ptx::smem_u32(&full_bar[st]), ph)) {
+            if (!failed && !ptx::mbar_wait(ptx::smem_u32(&full_bar[st]), ph)) {
                 if (lane == 0) atomicExch(p.status, 2);
                 failed = true;
-                break;
             }
-            if (warp_ok) consume_stage<F, BITS, SPARSE, MT>(kblock_info(p, kb), smem0 + st * SL::kBytes, L, acc, lut);
+            if (warp_ok && !failed) consume_stage<F, BITS, SPARSE, MT>(kblock_info(p, kb), smem0 + st * SL::kBytes, L, acc, lut);
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&empty_bar[st]));
             if (++st == kStages) { st = 0; ph ^= 1u; }
         }
-        if (failed) break;
-
         // ---- store: lane (g, t) holds, per m-tile, rows m = 2t (c0, c2) and m = 2t + 1 (c1, c3) of columns 4g .. 4g+3 ----
         const bool complete = (kb0 == 0) && (kb1 == p.KB);
         const int col = ct * kCTile + wc * 32 + L.g * 4;
@@ -671,8 +667,8 @@ static cudaError_t launch_one(const StreamParams& p, int max_ctas, cudaStream_t 
     using SL = StageLayout<Format<BITS, SPARSE>, MT>;
     const size_t smem = (size_t)kStages * SL::kBytes;
     auto kern = stream_kernel<BITS, SPARSE, MT>;
-    static int ctas_per_sm[16] = {0};                 // per device; benign race: every writer stores the same value
-    static int sm_count[16] = {0};
+    static std::atomic<int> ctas_per_sm[16];          // per device; concurrent first calls store the same values
+    static std::atomic<int> sm_count[16];
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;

@@ -22,6 +22,7 @@
 #include <stdexcept>
 #include <string>
 #include <utility>
+#include <vector>
 
 #include "../../include/int4matmul_b200.h"
 
@@ -34,16 +35,20 @@ using torch::Tensor;
         c10::optional<Tensor> sparse_mask
 #define I4_TENSOR_MULT_PASS outs, matrix, multiplier, scales, zeros, group_size, sparse_mask
 
+struct Workspace {
+    Tensor buffer;
+    cudaStream_t stream;
+};
 std::mutex g_ws_mutex;
-std::map<std::pair<int, int64_t>, Tensor> g_workspaces;
+std::map<std::pair<int, int64_t>, Workspace> g_workspaces;
 
 Tensor workspace_for(const c10::Device& dev, const c10::cuda::CUDAStream& stream) {
     std::lock_guard<std::mutex> lock(g_ws_mutex);
     const auto key = std::make_pair((int)dev.index(), (int64_t)stream.id());
     auto it = g_workspaces.find(key);
-    if (it != g_workspaces.end()) return it->second;
+    if (it != g_workspaces.end()) return it->second.buffer;
     Tensor ws = torch::zeros({(int64_t)i4mm_workspace_bytes()}, torch::dtype(torch::kUInt8).device(dev));
-    g_workspaces.emplace(key, ws);
+    g_workspaces.emplace(key, Workspace{ws, stream.stream()});
     return ws;
 }
 
@@ -153,9 +158,36 @@ void weight_matrix_packing(Tensor wt_outs, Tensor msk_outs, Tensor wt_in, Tensor
     }
 }
 
+// Not in the reference (its kernels have no waits): waits for every stream this module has launched on, on the
+// current device, and raises if a kernel gave up on one of its bounded device-side waits since the last check.
+// The multiply entries do not call it themselves, because it synchronises.
+void check_device_status() {
+    int dev = 0;
+    TORCH_CHECK(cudaGetDevice(&dev) == cudaSuccess, "no current CUDA device");
+    std::vector<Workspace> mine;
+    {
+        std::lock_guard<std::mutex> lock(g_ws_mutex);
+        for (auto& kv : g_workspaces)
+            if (kv.first.first == dev) mine.push_back(kv.second);
+    }
+    int worst = I4MM_OK;
+    for (auto& w : mine) {
+        const int st = i4mm_device_status(w.buffer.data_ptr(), (void*)w.stream);
+        if (st == I4MM_ERR_TIMEOUT) {                     // the scratch of a cut-short launch is not all-zero any more
+            w.buffer.zero_();
+            cudaDeviceSynchronize();
+        }
+        if (st != I4MM_OK) worst = st;
+    }
+    check_status(worst, "int4matmul device status");
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+    m.def("check_device_status", &check_device_status,
+          "raise if a kernel launched by this module gave up on a bounded device-side wait (synchronises)");
+
     m.def("weight_matrix_packing", &weight_matrix_packing, "int4_sparse_pack");
 
     m.def("quant_matmul", &quant_matmul, "intn_fp16_mult");

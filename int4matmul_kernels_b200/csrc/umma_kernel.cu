@@ -29,6 +29,8 @@
 #include <cuda.h>
 #include <dlfcn.h>
 
+#include <atomic>
+
 #include "common.cuh"
 #include "ptx.cuh"
 
@@ -36,16 +38,6 @@ namespace i4mm {
 
 namespace {
 
-#ifdef I4MM_TRACE
-#ifndef I4MM_TRACE_CTA
-#define I4MM_TRACE_CTA 0
-#endif
-// debug build only: CTA 0 records clock64() stamps into the tail of the partials scratch
-#define TRACE(role, idx, slot) do { if (blockIdx.x == I4MM_TRACE_CTA && (idx) < 64 && lane == 0) \
-    reinterpret_cast<long long*>(p.partials + (148 * 4 * 2 * 32 * 128) - 65536)[((role) * 64 + (idx)) * 8 + (slot)] = clock64(); } while (0)
-#else
-#define TRACE(role, idx, slot) do {} while (0)
-#endif
 
 enum : int { MODE_FAST = 0, MODE_GENERAL = 1, MODE_SLOW = 2 };
 
@@ -331,15 +323,12 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
     __shared__ __align__(8) Barriers bars;
     __shared__ uint4 lut[16];
     __shared__ uint32_t tmem_base_smem;
-    __shared__ volatile int s_abort;     // set by the MMA warp when it gives up, before it releases the epilogue warps for the last time
+    __shared__ volatile int s_abort;     // set by a warp that gives up on the accumulator (the MMA warp before it releases the epilogue
+                                         // warps for the last time; an epilogue warp before its group's next named barrier)
 
     // the shuffle tells the compiler that the warp index is warp-uniform: role dispatch, stage indices and barrier
     // addresses derived from it then live in uniform registers instead of costing vector-ALU instructions
     const int lane = threadIdx.x & 31, warp = __shfl_sync(0xFFFFFFFFu, (int)(threadIdx.x >> 5), 0);
-#ifdef I4MM_TRACE
-    long long trace_gt0, trace_c0 = clock64();
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(trace_gt0));
-#endif
     const uint32_t rank = PAIR ? ptx::cluster_ctarank() : 0u;       // in the pair; rank 0 leads (issues the MMAs, owns the pair's barriers)
     const uint32_t smem0 = (ptx::smem_u32(smem) + 1023u) & ~1023u;
     const uint32_t b_ring = smem0;
@@ -436,9 +425,7 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
                 const int u1 = (int)min(U, u0 + (t_hi - t));
                 const int ct = tile_ct(tile);
                 for (int u = u0; u < u1; ++u, ++si) {
-                    TRACE(0, (int)si, 0);
                     if (!ptx::mbar_wait_relaxed(ptx::smem_u32(&bars.w_empty[ws]), wph ^ 1u, 1600)) { atomicExch(p.status, 11); ok = false; break; }
-                    TRACE(0, (int)si, 1);
                     const uint32_t st = w_ring + ws * WS::kBytes, full = ptx::smem_u32(&bars.w_full[ws]);
                     ptx::mbar_arrive_expect_tx(full, kBytes);
                     ptx::tma_load_2d(st + WS::kW, &tm.w, ct * 128, u * 2 * F::WROWS, full);
@@ -448,7 +435,6 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
                         ptx::tma_load_2d(st + WS::kS, &tm.s, ct * 128, g0, full);
                         ptx::tma_load_2d(st + WS::kZ, &tm.z, ct * 128, g0, full);
                     }
-                    TRACE(0, (int)si, 2);
                     if (++ws == C::kWStages) { ws = 0; wph ^= 1u; }
                 }
                 t += u1 - u0;
@@ -518,23 +504,19 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
                 const long long tile = div_nn(t, U);
                 const int u0 = (int)(t - tile * U);
                 const int u1 = (int)min(U, u0 + (t_hi - t));
-                TRACE(3, (int)seg, 4);
                 if (!ptx::mbar_wait(ptx::smem_u32(&bars.d_empty), (seg & 1u) ^ 1u)) {
                     if (lane == 0) atomicExch(p.status, 21);
                     ok = false;
                     break;
                 }
-                TRACE(3, (int)seg, 5);
                 ptx::tc_fence_after_sync();
                 uint32_t s = si % kABStages, ph = (si / kABStages) & 1u;
                 for (int u = u0; u < u1; ++u, ++si) {
-                    TRACE(1, (int)si, 0);
                     if (!ptx::mbar_wait(ptx::smem_u32(&bars.ab_full[s]), ph)) {
                         if (lane == 0) atomicExch(p.status, 22);
                         ok = false;
                         break;
                     }
-                    TRACE(1, (int)si, 1);
                     ptx::tc_fence_after_sync();
                     const uint64_t bdesc = ptx::smem_desc_sw128(b_ring + s * kBStageBytes);
                     const uint32_t a0 = tmem_base + C::kACol0 + s * 64;
@@ -554,7 +536,6 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
                         }
                     }
                     __syncwarp();
-                    TRACE(1, (int)si, 2);
                     if (++s == kABStages) { s = 0; ph ^= 1u; }
                 }
                 if (!ok) break;
@@ -567,7 +548,6 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
                     }
                 }
                 __syncwarp();
-                TRACE(3, (int)seg, 6);
                 if (C::kEpiHandoff) {
                     // the epilogue warps sleep on a hardware barrier instead of polling for the whole segment
                     if (!ptx::mbar_wait(ptx::smem_u32(&bars.d_full), seg & 1u)) {
@@ -595,16 +575,22 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
             const int mt = tile_mt(tile), ct = tile_ct(tile);
             const int col = (warp & 3) * 32 + lane;
             const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
-            if (warp == kEpiWarp0 || (!C::kEpiWarps && warp == 0)) TRACE(3, (int)seg, 0);
             if (C::kEpiHandoff) {
                 ptx::named_bar_sync(2, 128 + 32);          // released by the MMA warp once the accumulator is complete
                 if (s_abort) return false;
-            } else if (!ptx::mbar_wait(ptx::smem_u32(&bars.d_full), seg & 1u)) {
-                if (lane == 0) atomicExch(p.status, 33);
-                return false;
+            } else {
+                bool got = ptx::mbar_wait(ptx::smem_u32(&bars.d_full), seg & 1u);
+                if (!got && lane == 0) atomicExch(p.status, 33);
+                if (C::kEpiTransposed) {
+                    // the four warps of an epilogue group meet at named barriers further down: a give-up has to be
+                    // the whole group's decision, or the warps that went on would wait there for ever
+                    if (!got) s_abort = 1;
+                    ptx::named_bar_sync(1 + 3 * ((warp - kEpiWarp0) >> 2), 128);
+                    got = s_abort == 0;
+                }
+                if (!got) return false;
             }
             ptx::tc_fence_after_sync();
-            if (warp == kEpiWarp0 || (!C::kEpiWarps && warp == 0)) TRACE(3, (int)seg, 1);
             const bool complete = (u0 == 0) && (u1 == (int)U);
             const int scol = ct * 128 + col;
             const bool col_ok = scol < p.S;
@@ -709,9 +695,13 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
                             continue;
                         }
 #pragma unroll
-                        for (int j = 0; j < 16; ++j)
-                            ptx::sts16(stage + (j0 - eg * kShare + j) * 256 + col * 2,
-                                       __half_as_ushort(__float2half_rn(__uint_as_float(v[j]))));
+                        for (int j = 0; j < 16; ++j) {
+                            float f = __uint_as_float(v[j]);
+                            // matvec route with many rows: add the caller's old value to the unrounded sum (one rounding)
+                            if (p.accumulate && col_ok && j0 + j < nrows)
+                                f += __half2float(p.out[(size_t)(row0 + j0 + j) * p.S + scol]);
+                            ptx::sts16(stage + (j0 - eg * kShare + j) * 256 + col * 2, __half_as_ushort(__float2half_rn(f)));
+                        }
                     }
                     ptx::named_bar_sync(bar_id, 128);
 #pragma unroll 1
@@ -749,8 +739,12 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
                         continue;
                     }
 #pragma unroll
-                    for (int j = 0; j < 16; ++j)
-                        ptx::sts16(stage_tile + j * 256 + col * 2, __half_as_ushort(__float2half_rn(__uint_as_float(v[j]))));
+                    for (int j = 0; j < 16; ++j) {
+                        float f = __uint_as_float(v[j]);
+                        if (p.accumulate && col_ok && j0 + j < nrows)
+                            f += __half2float(p.out[(size_t)(row0 + j0 + j) * p.S + scol]);
+                        ptx::sts16(stage_tile + j * 256 + col * 2, __half_as_ushort(__float2half_rn(f)));
+                    }
                     ptx::named_bar_sync(bar_id, 128);
 #pragma unroll
                     for (int r = 0; r < 2; ++r) {
@@ -799,7 +793,6 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
                 }
             }
             }
-            if (warp == kEpiWarp0 || (!C::kEpiWarps && warp == 0)) TRACE(3, (int)seg, 2);
             return true;
         };
 
@@ -842,7 +835,6 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
                 for (int u = u0 + (int)(((uint32_t)wg + (uint32_t)C::kWG - si0 % (uint32_t)C::kWG) % (uint32_t)C::kWG); u < u1; u += C::kWG) {
                     const uint32_t si = si0 + (uint32_t)(u - u0);
                     const uint32_t ws = si % C::kWStages, wph = (si / C::kWStages) & 1u;     // constants: multiply-shift, no division
-                    if (warp == 0) TRACE(2, (int)si, 0);
                     if (C::kWGuard && !ptx::mbar_wait(ptx::smem_u32(&bars.w_empty[ws]), wph ^ 1u)) {   // see Cfg::kWStages
                         if (lane == 0) atomicExch(p.status, 35);
                         ok = false;
@@ -853,7 +845,6 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
                         ok = false;
                         break;
                     }
-                    if (warp == 0) TRACE(2, (int)si, 1);
                     const uint32_t st = w_ring + ws * WS::kBytes;
                     const uint32_t g0 = p.gdiv(2u * (uint32_t)u);
                     const uint32_t as = si % kABStages, aph = (si / kABStages) & 1u;
@@ -890,7 +881,6 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
                             __syncwarp();
                             if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&bars.w_empty[ws]));   // both halves are in registers now
                         }
-                        if (warp == 0) TRACE(2, (int)si, 2 + 2 * h);
                         if (h == 0) {
                             if (C::kDeferArrive && pending >= 0) announce(pending);       // before any wait: the MMAs must be able to go on
                             // the A stage (and its activation tile) is free once the MMAs of its previous use have completed
@@ -901,14 +891,12 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
                             }
                             ptx::tc_fence_after_sync();
                         }
-                        if (warp == 0) TRACE(2, (int)si, 3 + 2 * h);
                         ptx::tmem_st32(lane_addr + C::kACol0 + as * 64 + h * 32, A);
                     }
                     if (!ok) break;
                     // (not deferred for the warpgroup's first stage: the pipeline is still filling and the MMA warp is waiting)
                     if (C::kDeferArrive && si >= (uint32_t)C::kWG) pending = (int)as;
                     else announce((int)as);
-                    if (warp == 0) TRACE(2, (int)si, 6);
                 }
                 if (!ok) break;
                 if (C::kDeferArrive && pending >= 0) { announce(pending); pending = -1; }
@@ -929,14 +917,6 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
         if (PAIR) ptx::tmem_dealloc_pair(tmem_base, C::kTmemCols);
         else ptx::tmem_dealloc(tmem_base, C::kTmemCols);
     }
-#ifdef I4MM_TRACE
-    if (threadIdx.x == 0 && blockIdx.x < 1024) {
-        long long gt1;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt1));
-        long long* rec = reinterpret_cast<long long*>(p.partials + (148 * 4 * 2 * 32 * 128) - 65536) + 4096 + blockIdx.x * 4;
-        rec[0] = trace_gt0; rec[1] = gt1; rec[2] = trace_c0; rec[3] = clock64();
-    }
-#endif
 }
 
 // Sums the K parts written by umma_kernel (fp32, (part, row, S)) in part order, rounds once to fp16, and puts the
@@ -999,6 +979,9 @@ bool encode_2d(CUtensorMap* out, const void* base, CUtensorMapDataType dt, int e
                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// what the last tcgen05 launch of this host thread chose: tile rows + 1000 if CTA pairs + 10000 * K parts (tests read it)
+thread_local int g_last_shape = 0;
+
 constexpr long long kPartialWords = 148LL * 4 * 32 * 128;      // 64-bit words of partial tiles in the workspace (capi.cu sizes it)
 
 // More than 32 rows and tiles that fill less than half of the GPU: cut K into parts so that
@@ -1046,8 +1029,9 @@ int launch_nt(const UmmaParams& p_in, const __half* x, int n_groups, cudaStream_
     const size_t smem = 1024 + (size_t)ABStages<NT, PAIR>::value * kBStageBytes + (size_t)C::kWStages * WStage<F>::kBytes +
                         (!C::kEpiTransposed ? 0 : PAIR ? NT * 256 : 4096 * ((C::kEpiGroups == 2 && NT < 256) ? 2 : 1));
     auto kern = umma_kernel<BITS, SPARSE, NT, PAIR>;
-    static int ctas_per_sm[16] = {0};
-    static int sm_count[16] = {0};
+    // per-device caches; atomics because two host threads may make their first call at once (both then compute the same values)
+    static std::atomic<int> ctas_per_sm[16];
+    static std::atomic<int> sm_count[16];
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) { *cuda_err = e; return I4MM_ERR_LAUNCH; }
@@ -1070,7 +1054,7 @@ int launch_nt(const UmmaParams& p_in, const __half* x, int n_groups, cudaStream_
     }
     if (PAIR) {
         // clusters of two CTAs; as many as can be resident at once, each walking its share of the pair tiles
-        static int max_clusters[16] = {0};
+        static std::atomic<int> max_clusters[16];
         cudaLaunchConfig_t cfg = {};
         cudaLaunchAttribute attr[1];
         attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -1103,6 +1087,7 @@ int launch_nt(const UmmaParams& p_in, const __half* x, int n_groups, cudaStream_
         e = cudaLaunchKernelEx(&cfg, kern, tm, p);
         if (e != cudaSuccess) { *cuda_err = e; return I4MM_ERR_LAUNCH; }
         count_launch();
+        g_last_shape = NT + 1000 + 10000 * p.kparts;
         if (p.kparts > 1) return launch_kparts_reduce(p, stream, cuda_err);
         return I4MM_OK;
     }
@@ -1117,6 +1102,7 @@ int launch_nt(const UmmaParams& p_in, const __half* x, int n_groups, cudaStream_
     e = cudaGetLastError();
     if (e != cudaSuccess) { *cuda_err = e; return I4MM_ERR_LAUNCH; }
     count_launch();
+    g_last_shape = NT + 10000 * p.kparts;
     if (p.kparts > 1) return launch_kparts_reduce(p, stream, cuda_err);
     return I4MM_OK;
 }
@@ -1145,18 +1131,20 @@ int choose_tile_rows(int rows, int col_tiles, int sms) {
 constexpr int kPairMinRows = 128;
 
 template <int BITS, bool SPARSE>
-int launch_fmt(UmmaParams& p, const __half* x, int n_groups, int pair_mode, cudaStream_t stream, cudaError_t* cuda_err) {
-    static int sms = 0;
+int launch_fmt(UmmaParams& p, const __half* x, int n_groups, int pair_mode, int force_nt, cudaStream_t stream, cudaError_t* cuda_err) {
+    static std::atomic<int> sms_of[16];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) dev = 0;
+    dev &= 15;
+    int sms = sms_of[dev].load();
     if (sms == 0) {
-        int dev = 0, n = 0;
-        if (cudaGetDevice(&dev) == cudaSuccess && cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0)
-            sms = n;
-        else
-            sms = 148;
+        int n = 0;
+        sms = (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0) ? n : 148;
+        sms_of[dev].store(sms);
     }
     // 128 rows or more (the whole-tile configurations) run as CTA pairs, two SMs per MMA, unless the caller asked for single CTAs
-    const bool pair = pair_mode == 0 && p.rows >= kPairMinRows;
-    const int nt = pair ? choose_tile_rows(p.rows, (p.CT + 1) / 2, sms / 2) : choose_tile_rows(p.rows, p.CT, sms);
+    const bool pair = pair_mode == 0 && (force_nt ? force_nt >= 128 : p.rows >= kPairMinRows);
+    const int nt = force_nt ? force_nt : pair ? choose_tile_rows(p.rows, (p.CT + 1) / 2, sms / 2) : choose_tile_rows(p.rows, p.CT, sms);
     p.MTILES = (p.rows + nt - 1) / nt;
     if (pair) {
         switch (nt) {
@@ -1182,13 +1170,16 @@ int launch_fmt(UmmaParams& p, const __half* x, int n_groups, int pair_mode, cuda
 
 }  // namespace
 
+int umma_last_shape() { return g_last_shape; }
+void umma_clear_last_shape() { g_last_shape = 0; }
+
 bool umma_supported(int bits, bool sparse, int total_rows, int N, int S) {
     (void)bits; (void)sparse; (void)S;
     return total_rows >= 1 && N >= 64 && encode_tiled_fn() != nullptr;
 }
 
 int umma_launch(int bits, bool sparse, const StreamParams& sp, int total_rows, int n_groups, int group_size, int cta_pairs /* 0 by shape, 1 never */,
-                cudaStream_t stream, cudaError_t* cuda_err) {
+                int force_nt /* 0 = by shape */, cudaStream_t stream, cudaError_t* cuda_err) {
     (void)group_size;
     UmmaParams p{};
     p.out = sp.out;
@@ -1205,10 +1196,10 @@ int umma_launch(int bits, bool sparse, const StreamParams& sp, int total_rows, i
     p.CT = sp.CT;
     p.accumulate = sp.accumulate;
     p.gdiv = sp.gdiv;
-    if (sparse) return launch_fmt<4, true>(p, sp.x, n_groups, cta_pairs, stream, cuda_err);
-    if (bits == 4) return launch_fmt<4, false>(p, sp.x, n_groups, cta_pairs, stream, cuda_err);
-    if (bits == 3) return launch_fmt<3, false>(p, sp.x, n_groups, cta_pairs, stream, cuda_err);
-    return launch_fmt<2, false>(p, sp.x, n_groups, cta_pairs, stream, cuda_err);
+    if (sparse) return launch_fmt<4, true>(p, sp.x, n_groups, cta_pairs, force_nt, stream, cuda_err);
+    if (bits == 4) return launch_fmt<4, false>(p, sp.x, n_groups, cta_pairs, force_nt, stream, cuda_err);
+    if (bits == 3) return launch_fmt<3, false>(p, sp.x, n_groups, cta_pairs, force_nt, stream, cuda_err);
+    return launch_fmt<2, false>(p, sp.x, n_groups, cta_pairs, force_nt, stream, cuda_err);
 }
 
 }  // namespace i4mm

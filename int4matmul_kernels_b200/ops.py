@@ -48,6 +48,27 @@ def workspace(device: torch.device, stream: torch.cuda.Stream) -> torch.Tensor:
     return ws
 
 
+def check_device_status(device: torch.device | None = None) -> None:
+    """Waits for every stream `workspace()` has served on `device` and raises Int4MatmulError(ERR_TIMEOUT) if a
+    kernel gave up on one of its bounded device-side waits since the last check (the results of that launch are
+    void).  Not called by the multiply entries themselves, because it synchronises; no reference counterpart."""
+    index = torch.cuda.current_device() if device is None or device.index is None else device.index
+    lib = capi.load()
+    worst = capi.OK
+    with torch.cuda.device(index):
+        for (dev, stream), ws in list(_workspaces.items()):
+            if dev != index:
+                continue
+            status = lib.i4mm_device_status(ws.data_ptr(), stream)
+            if status == capi.ERR_TIMEOUT:
+                ws.zero_()            # the scratch of a cut-short launch is not all-zero any more
+                torch.cuda.synchronize(index)
+            if status != capi.OK:
+                worst = status
+    if worst != capi.OK:
+        raise Int4MatmulError(worst, "int4matmul device status")
+
+
 def _mult(bits: int, route: str, outs, matrix, multiplier, scales, zeros, group_size, sparse_mask, path: int) -> None:
     if bits not in (4, 3, 2):
         raise ValueError("Unsupported bit width for " +

@@ -36,7 +36,9 @@ def quantize_groupwise(weight: torch.Tensor, bits: int = 4, group_size: int = 12
     wg = w.view(n // g, g, s)
     lo = wg.amin(dim=1).clamp(max=0.0)
     hi = wg.amax(dim=1).clamp(min=0.0)
-    scale = ((hi - lo) / levels).clamp(min=1e-8).to(torch.float16)
+    # clamped after the cast: a tiny fp32 scale would underflow to 0 in fp16, and an all-zero group (zero-padded
+    # columns, a fully pruned block) would turn into 0 / 0.  2^-14 is the smallest normal fp16.
+    scale = ((hi - lo) / levels).to(torch.float16).clamp(min=2.0 ** -14)
     zero = torch.round(-lo / scale.float()).clamp(0, levels).to(torch.float16)
     q = torch.round(wg / scale.float()[:, None, :]) + zero.float()[:, None, :]
     q = q.clamp(0, levels).to(torch.uint8).view(n, s)

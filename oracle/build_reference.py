@@ -12,7 +12,15 @@ Two things stand between the sources and a current toolchain, both handled from 
 The dense int3 matvec kernel does not assemble for sm_100 (ptxas C7600 at -O1..-O3), so matvec_kernel.cu is
 assembled with `-Xptxas -O1` first and, if that fails, with `-Xptxas -O0`; the module records which.
 
-Usage:  python oracle/build_reference.py [/path/to/reference]      (default /root/reference)
+A second module, `int4matmul_ref_timing`, exists only so that the reference's matvec kernels can be TIMED as the
+compiler would normally build them: its matvec translation unit is compiled at default optimisation from a
+build directory (oracle/_ref/shadow/) that holds symbolic links to the reference's matvec_kernel.cu and
+matmul.cuh and a kernel_specs.cuh generated from the reference's list with the dense int3 row filtered out
+(a quoted #include is looked up beside the including file first, so the list beside the links is the one found).
+In that module the dense int3 matvec launches nothing; every other kernel is the reference's own.
+
+Usage:  python oracle/build_reference.py [/path/to/reference]
+        (default: $INT4MATMUL_REFERENCE_DIR, else a checkout named `reference` beside this repository)
 """
 import os
 import subprocess
@@ -44,7 +52,8 @@ def main(ref_dir: str) -> int:
     target = os.path.join(OUT, "int4matmul_ref" + suffix)
     sources = ["int4matmul.cpp", "matmul_kernel.cu", "matvec_kernel.cu", "utils_kernel.cu"]
     newest_src = max(os.path.getmtime(os.path.join(ref_dir, s)) for s in sources + ["matmul.cuh", "kernel_specs.cuh"])
-    if os.path.exists(target) and os.path.getmtime(target) > newest_src:
+    timing = os.path.join(OUT, "int4matmul_ref_timing" + suffix)
+    if all(os.path.exists(t) and os.path.getmtime(t) > newest_src for t in (target, timing)):
         print("[ref] up to date:", target)
         return 0
     inc = []
@@ -81,17 +90,62 @@ def main(ref_dir: str) -> int:
             print(out[-3000:])
             return 1
     torch_lib = os.path.join(os.path.dirname(torch.__file__), "lib")
-    link = ["nvcc", "-shared", "-o", target, *objs, "-L", torch_lib, "-lc10", "-lc10_cuda", "-ltorch_cpu", "-ltorch_cuda",
-            "-ltorch", "-ltorch_python", "-Xlinker", f"-rpath={torch_lib}"]
+    libs = ["-L", torch_lib, "-lc10", "-lc10_cuda", "-ltorch_cpu", "-ltorch_cuda", "-ltorch", "-ltorch_python",
+            "-Xlinker", f"-rpath={torch_lib}"]
+    link = ["nvcc", "-shared", "-o", target, *objs, *libs]
     r = subprocess.run(link, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
     if r.returncode != 0:
         print(r.stdout[-3000:])
         return 1
+    # ---- the timing module: matvec translation unit at default optimisation, without the dense int3 row ----
+    shadow = os.path.join(OUT, "shadow")
+    os.makedirs(shadow, exist_ok=True)
+    for name in ("matvec_kernel.cu", "matmul.cuh"):
+        link_path = os.path.join(shadow, name)
+        if os.path.lexists(link_path):
+            os.remove(link_path)
+        os.symlink(os.path.join(ref_dir, name), link_path)
+    with open(os.path.join(ref_dir, "kernel_specs.cuh")) as f:
+        rows = [ln for ln in f.read().splitlines() if ln.replace(" ", "") != "MACRO_OP(false,3)"]
+    with open(os.path.join(shadow, "kernel_specs.cuh"), "w") as f:
+        f.write("\n".join(rows) + "\n")
+    timing_target = os.path.join(OUT, "int4matmul_ref_timing" + suffix)
+    tbase = [a.replace("int4matmul_ref", "int4matmul_ref_timing") if a.startswith("-DTORCH_EXTENSION_NAME") else a for a in base]
+    tobjs = []
+    ok = True
+    for s in sources:
+        src = os.path.join(shadow if s == "matvec_kernel.cu" else ref_dir, s)
+        obj = os.path.join(OUT, "obj", "timing_" + s.replace(".", "_") + ".o")
+        if s in ("matmul_kernel.cu", "utils_kernel.cu"):           # no module name inside: the objects above serve
+            tobjs.append(os.path.join(OUT, "obj", s.replace(".", "_") + ".o"))
+            continue
+        r = subprocess.run(tbase + ["-c", src, "-o", obj], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+        if r.returncode != 0:
+            notes.append("timing module not built: " + s + " failed at default optimisation")
+            print(r.stdout[-2000:])
+            ok = False
+            break
+        tobjs.append(obj)
+    if ok:
+        r = subprocess.run(["nvcc", "-shared", "-o", timing_target, *tobjs, *libs],
+                           stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+        if r.returncode != 0:
+            print(r.stdout[-3000:])
+            notes.append("timing module not linked")
+        else:
+            notes.append("int4matmul_ref_timing: matvec_kernel.cu at default ptxas optimisation, dense int3 matvec left out")
     with open(os.path.join(OUT, "BUILD_NOTES.txt"), "w") as f:
         f.write("\n".join(notes) + ("\n" if notes else "built with default flags\n"))
     print("[ref] built", target, "|", "; ".join(notes) if notes else "default flags")
     return 0
 
 
+def default_reference_dir() -> str:
+    env = os.environ.get("INT4MATMUL_REFERENCE_DIR")
+    if env:
+        return env
+    return os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
+
+
 if __name__ == "__main__":
-    sys.exit(main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference"))
+    sys.exit(main(sys.argv[1] if len(sys.argv) > 1 else default_reference_dir()))

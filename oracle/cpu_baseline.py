@@ -46,3 +46,24 @@ def timed_pass(problem: dict, rows: int, threads: int):
     _ = float(y.flatten()[0])
     t2 = time.perf_counter()
     return t1 - t0, t2 - t1
+
+
+def synthetic_unpacked(bits: int, n: int, s: int, m: int, group_size: int, sparse: bool = False, seed: int = 0) -> dict:
+    """A seeded problem in the UNPACKED form the comparator above starts from (the reference's test script also
+    dequantises from the unpacked weights it drew, kernel_test.py:126-157), with the benchmark's value
+    distributions; drawn as uint8 so that a 16384 x 16384 matrix costs 268 MB, not gigabytes."""
+    from . import reference_oracle as oracle
+    rng = np.random.default_rng(seed)
+    lo, hi = (0.002, 0.02) if bits == 4 else (0.005, 0.05)
+    g = n if group_size < 0 else group_size
+    n_groups = (n + g - 1) // g
+    q = rng.integers(0, 1 << bits, size=(n, s), dtype=np.uint8)
+    scales = rng.uniform(lo, hi, size=(n_groups, s)).astype(np.float16)
+    zeros = rng.integers(0, 1 << bits, size=(n_groups, s)).astype(np.float16)
+    x = rng.standard_normal(size=(1, m, n), dtype=np.float32).astype(np.float16)
+    keep = None
+    if sparse:
+        words = oracle.random_keep_words(rng, (n // 32, s)).view(np.uint32)
+        keep = ((words[:, None, :] >> np.arange(32, dtype=np.uint32)[None, :, None]) & 1).astype(bool).reshape(n, s)
+    return dict(bits=bits, n=n, s=s, m=m, batch=1, group_size=group_size, sparse=sparse, q=q, keep=keep,
+                scales=scales, zeros=zeros, x=x)

@@ -283,3 +283,59 @@ def expected(problem: dict, outs_in: np.ndarray | None = None):
     p = problem
     w16 = dequant_w16(p["bits"], p["q"], p["scales"], p["zeros"], p["group_size"], p["keep"])
     return matmul_ref(p["x"], w16, outs_in), w16, matmul_abs_bound(p["x"], w16)
+
+
+# --------------------------------------------------------------------------------------------
+# checks on sampled output columns (full-size shapes, where a whole-matrix oracle would take minutes)
+# --------------------------------------------------------------------------------------------
+
+def unpack_columns(bits: int, matrix: np.ndarray, mask: np.ndarray | None, cols: np.ndarray):
+    """(q uint8 (N, len(cols)), keep bool or None) of the chosen output columns of a packed matrix: every
+    output column depends only on its own column of the weight-side tensors (matmul_kernel.cu:258-267)."""
+    sub = np.ascontiguousarray(matrix[:, cols])
+    if mask is not None:
+        return unpack_sparse_int4(sub, np.ascontiguousarray(mask[:, cols]))
+    if bits == 3:
+        return unpack_dense_int3(sub), None
+    return unpack_dense_pow2(bits, sub), None
+
+
+def expected_columns(bits: int, matrix: np.ndarray, mask: np.ndarray | None, scales: np.ndarray, zeros: np.ndarray,
+                     group_size: int, x: np.ndarray, cols: np.ndarray, outs_in: np.ndarray | None = None):
+    """Reference-semantics result for the output columns `cols` only, computed from the PACKED tensors.
+
+    x (B, M, N) fp16; returns (want fp16 (B, M, len(cols)), abs bound (B, M, len(cols))).  outs_in, if given, is
+    the (B, M, len(cols)) slice of the caller's `outs` that the matvec route adds to (matvec_kernel.cu:351)."""
+    cols = np.asarray(cols)
+    q, keep = unpack_columns(bits, matrix, mask, cols)
+    w16 = dequant_w16(bits, q, scales[:, cols], zeros[:, cols], group_size, keep)
+    return matmul_ref(x, w16, outs_in), matmul_abs_bound(x, w16)
+
+
+def random_keep_words(rng: np.random.Generator, shape, pool: int = 1 << 16) -> np.ndarray:
+    """int32 keep-mask words with exactly 16 of 32 bits set, drawn from a pool of `pool` masks whose kept
+    positions are uniformly random 16-subsets (argsort of uniforms), so that large masks cost no large sort."""
+    order = np.argsort(rng.random(size=(pool, 32)), axis=1)
+    bits = (order < 16).astype(np.uint64) << np.arange(32, dtype=np.uint64)[None, :]
+    words = bits.sum(axis=1).astype(np.uint32)
+    return words[rng.integers(0, pool, size=shape)].view(np.int32)
+
+
+def make_packed_problem(bits: int, n: int, s: int, m: int, group_size: int, *, sparse: bool = False,
+                        batch: int = 1, seed: int = 0):
+    """Seeded problem for full-size shapes, drawn directly in the packed formats (uniform packed words are
+    uniform weights in every format: nibbles, crumbs, 3-bit fields of the 96-bit streams, compacted nibbles),
+    with the value distributions of make_problem.  No (N, S) array of unpacked weights is ever built; check
+    results with expected_columns."""
+    rng = np.random.default_rng(seed)
+    lo, hi = (0.002, 0.02) if bits == 4 else (0.005, 0.05)
+    rows = n // 16 if sparse else n * bits // 32
+    matrix = rng.integers(0, 1 << 32, size=(rows, s), dtype=np.uint64).astype(np.uint32).view(np.int32)
+    mask = random_keep_words(rng, (n // 32, s)) if sparse else None
+    g = n if group_size < 0 else group_size
+    n_groups = (n + g - 1) // g
+    scales = rng.uniform(lo, hi, size=(n_groups, s)).astype(np.float16)
+    zeros = rng.integers(0, 1 << bits, size=(n_groups, s)).astype(np.float16)
+    x = rng.standard_normal(size=(batch, m, n), dtype=np.float32).astype(np.float16)
+    return dict(bits=bits, n=n, s=s, m=m, batch=batch, group_size=group_size, sparse=sparse,
+                matrix=matrix, mask=mask, scales=scales, zeros=zeros, x=x)

@@ -64,4 +64,6 @@ def main(ref_dir: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2 and not os.environ.get("INT4MATMUL_REFERENCE_DIR"):
+        sys.exit("usage: make_golden.py /path/to/reference   (or set INT4MATMUL_REFERENCE_DIR)")
+    main(sys.argv[1] if len(sys.argv) > 1 else os.environ["INT4MATMUL_REFERENCE_DIR"])

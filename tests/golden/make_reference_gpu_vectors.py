@@ -2,7 +2,7 @@
 
 Needs the reference built by oracle/build_reference.py (oracle/_ref/int4matmul_ref*.so) and a CUDA device:
 
-    python tests/golden/make_reference_gpu_vectors.py gpurun_out/reference_gpu_vectors.npz
+    python tests/golden/make_reference_gpu_vectors.py OUTPUT.npz
 
 For seeded problems (inputs are regenerated from the seed by oracle.reference_oracle.make_problem, so only
 the outputs are stored) it runs the reference's `quant_matmul` (matvec and matmul routes, every supported
@@ -76,4 +76,6 @@ def main(out_path):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else os.path.join(ROOT, "gpurun_out", "reference_gpu_vectors.npz"))
+    if len(sys.argv) < 2:
+        sys.exit("usage: make_reference_gpu_vectors.py OUTPUT.npz")
+    main(sys.argv[1])

@@ -114,3 +114,31 @@ def test_matvec_accumulates_into_outs():
     acc = p["x"].reshape(1, -1).astype(np.float32) @ w16.astype(np.float32)
     assert np.array_equal(y1.reshape(-1), (acc.reshape(-1) + np.float32(2.5)).astype(np.float16))
     assert not np.array_equal(y0, y1)
+
+
+@pytest.mark.parametrize("bits,sparse", [(4, False), (3, False), (2, False), (4, True)])
+def test_sampled_columns_agree_with_the_whole_matrix(bits, sparse):
+    """expected_columns works from the packed tensors and must give, column for column, what expected() gives
+    from the unpacked weights, for both routes."""
+    p = o.make_problem(bits, 512, 256, 5, 64, sparse=sparse, seed=3, exponent_frac=0.2)
+    cols = np.array([0, 5, 77, 128, 255])
+    want, _, bound = o.expected(p)
+    w2, b2 = o.expected_columns(bits, p["matrix"], p["mask"], p["scales"], p["zeros"], 64, p["x"], cols)
+    assert np.array_equal(w2.view(np.uint16), want[..., cols].view(np.uint16))
+    assert np.allclose(b2, bound[..., cols])
+    base = np.random.default_rng(1).standard_normal(want.shape).astype(np.float16)
+    want_acc, _, _ = o.expected(p, outs_in=base)
+    w3, _ = o.expected_columns(bits, p["matrix"], p["mask"], p["scales"], p["zeros"], 64, p["x"], cols, base[..., cols])
+    assert np.array_equal(w3.view(np.uint16), want_acc[..., cols].view(np.uint16))
+
+
+def test_packed_problem_generator():
+    p = o.make_packed_problem(4, 256, 128, 3, 64, sparse=True, seed=9)
+    assert p["matrix"].shape == (16, 128) and p["mask"].shape == (8, 128) and p["x"].shape == (1, 3, 256)
+    bits = np.unpackbits(p["mask"].view(np.uint8).reshape(-1, 4), axis=1)
+    assert (bits.sum(axis=1) == 16).all()                      # exactly 16 of every 32 kept (utils_kernel.cu:41)
+    q, keep = o.unpack_sparse_int4(p["matrix"], p["mask"])
+    assert keep.reshape(8, 32, 128).sum(axis=1).min() == 16 and q.max() <= 15
+    for b, rows in ((4, 32), (3, 24), (2, 16)):
+        d = o.make_packed_problem(b, 256, 64, 1, -1, seed=b)
+        assert d["matrix"].shape == (rows, 64) and d["scales"].shape == (1, 64) and d["zeros"].max() < (1 << b)

@@ -33,6 +33,17 @@ def test_sparse_quantiser_keeps_the_16_largest_of_every_32():
     assert (kept_min >= drop_max).all()
 
 
+def test_all_zero_group_quantises_to_exact_zeros():
+    w = torch.randn((256, 128), generator=torch.Generator().manual_seed(5)) * 0.05
+    w[64:128, :] = 0.0                      # a whole group of every column
+    w[:, 7] = 0.0                           # a zero-padded column
+    qz = quantize.quantize_groupwise(w, 4, 64)
+    assert torch.isfinite(qz["scales"].float()).all() and (qz["scales"] > 0).all()
+    w16 = quantize.dequantize(qz["q"], qz["scales"], qz["zeros"], 64)
+    assert torch.isfinite(w16.float()).all()
+    assert (w16[64:128, :] == 0).all() and (w16[:, 7] == 0).all()
+
+
 def test_quantiser_rejects_bad_shapes():
     with pytest.raises(ValueError):
         quantize.quantize_groupwise(torch.zeros((100, 64)), 4, 64)
