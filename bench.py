@@ -319,6 +319,8 @@ def run_stack(args):
         # a short collective timeout: a rank that never arrives ends the run with an error instead of a long hang
         dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=90))
     capi.load()
+    from int4matmul_kernels_b200 import ops
+    ops.set_static_weights(True)
     stack = sharding.DecoderStack(cfg, rank, world, dev)
     gen = torch.Generator().manual_seed(4321)
     h_host = torch.randn((m, cfg.hidden), generator=gen).to(torch.float16).pin_memory()
@@ -767,7 +769,7 @@ def main():
 
     import torch
     import torch.distributed as dist
-    from int4matmul_kernels_b200 import capi
+    from int4matmul_kernels_b200 import capi, ops
     import int4matmul_kernels_b200 as pkg
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -781,7 +783,10 @@ def main():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
     capi.load()                                   # fails loudly if the CUDA library is missing
+    # the benchmark's weights are never rewritten: launches may overlap the tail of the kernel before them
+    ops.set_static_weights(True)
     ctx = dict(torch=torch, dist=dist, dev=dev, world=world, rank=rank, local_rank=local_rank, ext=pkg.load_extension())
+    ctx["ext"].set_static_weights(True)
 
     line = run_workload(args, args.workload, w, ctx)
     if args.workload == DEFAULT_WORKLOAD and not args.no_matvec:

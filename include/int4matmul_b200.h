@@ -85,7 +85,13 @@ size_t i4mm_workspace_bytes(void);
  *   With path 2 or 3, `path | (T << 8)` also fixes the rows per tile (the MMA's N) to T in {16, 32, 64, 128, 160, 192,
  *   224, 256} instead of choosing it by shape (T >= 128 with path 2 runs as CTA pairs; T <= 64 needs rows <= T):
  *   for tests and tuning, results do not depend on it beyond fp32 summation order.
+ *   `path | I4MM_PATH_STATIC_WEIGHTS` is the caller's promise that matrix, mask, scales and zeros are not written by
+ *   the kernel that precedes this call in the stream (weights of a loaded model never are).  The tcgen05 kernel is then
+ *   launched so that its set-up and its first weight copies overlap the tail of that kernel (programmatic dependent
+ *   launch); it still waits for that kernel before it reads x, reads or writes out, or touches the workspace.  Without
+ *   the flag every launch is ordered after the whole preceding kernel, as the reference's launches are.
  */
+#define I4MM_PATH_STATIC_WEIGHTS 0x100000
 int i4mm_quant_matmul(int bits, int accumulate, int path,
                       void* out, const void* matrix, const void* mask /* NULL = dense */,
                       const void* x, const void* scales, const void* zeros,

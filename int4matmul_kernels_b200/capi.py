@@ -15,6 +15,7 @@ ERR_BITS, ERR_UNSUPPORTED, ERR_SHAPE, ERR_NULL, ERR_ALIGN = 1, 2, 3, 4, 5
 ERR_WORKSPACE, ERR_LAUNCH, ERR_MASK, ERR_DEVICE, ERR_TIMEOUT, ERR_TOO_LARGE = 6, 7, 8, 9, 10, 11
 
 PATH_AUTO, PATH_STREAM, PATH_TCGEN05, PATH_TCGEN05_SINGLE_CTA = 0, 1, 2, 3
+PATH_STATIC_WEIGHTS = 0x100000      # I4MM_PATH_STATIC_WEIGHTS: or-ed into a path (see the header)
 
 # every symbol the header declares, with its ctypes signature
 _SIGNATURES = {

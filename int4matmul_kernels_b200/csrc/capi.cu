@@ -20,7 +20,7 @@ cudaError_t check_mask_launch(const void* mask, size_t count, void* violations, 
 cudaError_t rownorm_launch(int mode, void* y, const void* a, const void* b, const void* c, long long rows, int width,
                            long long sa, long long sb, long long sc, cudaStream_t stream);
 int umma_launch(int bits, bool sparse, const StreamParams& p, int total_rows, int n_groups, int group_size, int cta_pairs,
-                int force_nt, cudaStream_t stream, cudaError_t* cuda_err);
+                int force_nt, int overlap, cudaStream_t stream, cudaError_t* cuda_err);
 bool umma_supported(int bits, bool sparse, int total_rows, int N, int S);
 }  // namespace i4mm
 
@@ -90,7 +90,8 @@ int i4mm_quant_matmul(int bits, int accumulate, int path,
         (mask && !aligned16(mask)))
         return I4MM_ERR_ALIGN;
     // bits 8.. of `path`: rows per tile to use on the tcgen05 path instead of the choice by shape (tests, tuning)
-    const int force_nt = path >= 0 ? path >> 8 : 0;
+    const int overlap = path >= 0 ? (path >> 20) & 1 : 0;         // I4MM_PATH_STATIC_WEIGHTS
+    const int force_nt = path >= 0 ? (path >> 8) & 0xFFF : 0;
     if (path >= 0) path &= 0xFF;
     if (path < 0 || path > 3) return I4MM_ERR_SHAPE;
     if (force_nt != 0) {
@@ -132,7 +133,7 @@ int i4mm_quant_matmul(int bits, int accumulate, int path,
     }
     if (use_umma) {
         cudaError_t ce = cudaSuccess;
-        const int rc = i4mm::umma_launch(bits, sparse, p, (int)rows, (int)n_groups, (int)(group_size < 0 ? -1 : group_size), path == 3 ? 1 : 0, force_nt, st, &ce);
+        const int rc = i4mm::umma_launch(bits, sparse, p, (int)rows, (int)n_groups, (int)(group_size < 0 ? -1 : group_size), path == 3 ? 1 : 0, force_nt, overlap, st, &ce);
         if (rc == I4MM_ERR_LAUNCH) return fail_cuda(ce);
         return rc;
     }

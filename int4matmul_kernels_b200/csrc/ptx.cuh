@@ -76,6 +76,11 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, int 
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                  ::"r"(dst), "l"(tmap), "r"(x), "r"(y), "r"(bar) : "memory");
 }
+// 3-D tiled tensor-map copy, coordinates (x = innermost, y, z)
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const void* tmap, int x, int y, int z, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+                 ::"r"(dst), "l"(tmap), "r"(x), "r"(y), "r"(z), "r"(bar) : "memory");
+}
 __device__ __forceinline__ void prefetch_tmap(const void* tmap) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
 }
@@ -91,6 +96,14 @@ __device__ __forceinline__ bool elect_one() {
         : "=r"(pred));
     return pred != 0;
 }
+
+// ---- programmatic dependent launch --------------------------------------------------------------------------
+// A kernel launched with the programmatic-stream-serialization attribute may start while the kernel before it in the
+// stream is still running.  wait: returns once that kernel has completed and its writes are visible (at once when the
+// launch had no such attribute).  launch_dependents: the next kernel in the stream may be scheduled as soon as every
+// CTA of this grid has said so or exited.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 // ---- named barrier over a subset of the CTA's warps ----------------------------------------------------
 __device__ __forceinline__ void named_bar_arrive(uint32_t id, uint32_t threads) {

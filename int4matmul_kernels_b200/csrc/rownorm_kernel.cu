@@ -4,6 +4,7 @@
 // Inputs are fp16 rows of `width` elements with their own row strides (gathered q | k | v and gate | up are column
 // slices of one buffer); the output is contiguous.  No counterpart in the reference, which has no model code.
 #include "common.cuh"
+#include "ptx.cuh"
 
 namespace i4mm {
 
@@ -25,6 +26,11 @@ __global__ void __launch_bounds__(256) rownorm_kernel(__half* __restrict__ y, co
                                                       const __half* __restrict__ b, const __half* __restrict__ c,
                                                       int width, long long sa, long long sb, long long sc) {
     __shared__ float red[32];
+    // Launched with programmatic stream serialization: the kernel after this one may be scheduled at once (a multiply
+    // then sets itself up and starts copying weights meanwhile), and nothing is read or written here before the kernel
+    // before this one has completed.
+    ptx::grid_launch_dependents();
+    ptx::grid_dependency_wait();
     const long long row = blockIdx.x;
     const __half2* a2 = reinterpret_cast<const __half2*>(a + row * sa);
     const __half2* b2 = MODE != 0 ? reinterpret_cast<const __half2*>(b + row * sb) : nullptr;
@@ -68,17 +74,26 @@ __global__ void __launch_bounds__(256) rownorm_kernel(__half* __restrict__ y, co
 cudaError_t rownorm_launch(int mode, void* y, const void* a, const void* b, const void* c, long long rows, int width,
                            long long sa, long long sb, long long sc, cudaStream_t stream) {
     if (rows <= 0) return cudaSuccess;
-    const dim3 grid((unsigned)rows), block(256);
     __half* yy = (__half*)y;
     const __half *aa = (const __half*)a, *bb = (const __half*)b, *cc = (const __half*)c;
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.gridDim = dim3((unsigned)rows, 1, 1);
+    cfg.blockDim = dim3(256, 1, 1);
+    cfg.stream = stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e;
     switch (mode) {
-        case 0: rownorm_kernel<0><<<grid, block, 0, stream>>>(yy, aa, bb, cc, width, sa, sb, sc); break;
-        case 1: rownorm_kernel<1><<<grid, block, 0, stream>>>(yy, aa, bb, cc, width, sa, sb, sc); break;
-        case 2: rownorm_kernel<2><<<grid, block, 0, stream>>>(yy, aa, bb, cc, width, sa, sb, sc); break;
-        default: rownorm_kernel<3><<<grid, block, 0, stream>>>(yy, aa, bb, cc, width, sa, sb, sc); break;
+        case 0: e = cudaLaunchKernelEx(&cfg, rownorm_kernel<0>, yy, aa, bb, cc, width, sa, sb, sc); break;
+        case 1: e = cudaLaunchKernelEx(&cfg, rownorm_kernel<1>, yy, aa, bb, cc, width, sa, sb, sc); break;
+        case 2: e = cudaLaunchKernelEx(&cfg, rownorm_kernel<2>, yy, aa, bb, cc, width, sa, sb, sc); break;
+        default: e = cudaLaunchKernelEx(&cfg, rownorm_kernel<3>, yy, aa, bb, cc, width, sa, sb, sc); break;
     }
-    count_launch();
-    return cudaGetLastError();
+    if (e == cudaSuccess) count_launch();
+    return e;
 }
 
 }  // namespace i4mm

@@ -17,6 +17,7 @@
 #include <c10/cuda/CUDAGuard.h>
 #include <c10/cuda/CUDAStream.h>
 
+#include <atomic>
 #include <map>
 #include <mutex>
 #include <stdexcept>
@@ -61,6 +62,11 @@ void check_status(int status, const char* what) {
 }
 
 enum class Route { AUTO, MATMUL, MATVEC };
+
+// Not in the reference: the caller's promise that the weight-side tensors are never written by the kernel that
+// precedes a multiply in the stream (weights of a loaded model), which lets a launch begin while that kernel finishes.
+std::atomic<bool> g_static_weights{false};
+void set_static_weights(bool flag) { g_static_weights.store(flag); }
 
 void quant_mult(uint32_t bits, Route route, I4_TENSOR_MULT_ARGS) {
     if (bits != 4 && bits != 3 && bits != 2) {
@@ -113,7 +119,7 @@ void quant_mult(uint32_t bits, Route route, I4_TENSOR_MULT_ARGS) {
     auto stream = c10::cuda::getCurrentCUDAStream(dev.index());
     Tensor ws = workspace_for(dev, stream);
     const int status = i4mm_quant_matmul(
-        (int)bits, matvec ? 1 : 0, /*path=*/0, outs.data_ptr(), matrix.data_ptr(), mask_ptr, multiplier.data_ptr(),
+        (int)bits, matvec ? 1 : 0, /*path=*/g_static_weights.load() ? I4MM_PATH_STATIC_WEIGHTS : 0, outs.data_ptr(), matrix.data_ptr(), mask_ptr, multiplier.data_ptr(),
         scales.data_ptr(), zeros.data_ptr(), batch * seq_len, in_size, out_size, scales.size(0), group_size,
         ws.data_ptr(), (size_t)ws.numel(), (void*)stream.stream());
     check_status(status, "int4matmul");
@@ -185,6 +191,8 @@ void check_device_status() {
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+    m.def("set_static_weights", &set_static_weights,
+          "declare that weight-side tensors are never written by the kernel preceding a multiply in the stream");
     m.def("check_device_status", &check_device_status,
           "raise if a kernel launched by this module gave up on a bounded device-side wait (synchronises)");
 

@@ -4,23 +4,24 @@
 // (matvec_kernel.cu:198-267).  Per CTA tile: 128 weight columns (S) on the 128 tensor-memory lanes x NT
 // activation rows on the MMA's N dimension, accumulated in fp32 in tensor memory over all of N (in-features).
 //
-//   weight producer   one thread: tensor-map copies (TMA) of the packed weight rows, the keep mask and the groups'
-//                     scales / zeros of one 128-k unit into a shared-memory ring (the scales / zeros come from a
-//                     thread of their own in the weight-streaming configuration)
-//   activation prod.  one thread: the activation tile (NT rows x 128 k as two 128-byte-swizzled sub-tiles)
+//   weight producer   one thread (two, in two warps, for the weight-streaming shapes): tensor-map copies (TMA) of the
+//                     packed weight rows, the keep mask and the groups' scales / zeros of one unit (128 k; 256 k for
+//                     the weight-streaming shapes) into a shared-memory ring
+//   activation prod.  one thread: the activation tile (NT rows x one unit of k as 128-byte-swizzled sub-tiles of 64 k);
+//                     for dense int4 weight streaming the whole warp, which reorders k inside the tile (see UFormat)
 //   dequant warps     warpgroups of 4 warps take the units in turn; thread i of a group owns weight column i: reads
-//                     its packed words from shared memory, rebuilds fp16((q - zero) * scale) in registers, in natural
-//                     k order, and writes them into its own tensor-memory lane with tcgen05.st (one packed int32 =
-//                     8 consecutive k of one column, which is exactly what a lane of the A operand holds)
-//   MMA warp          one elected thread issues 8 x tcgen05.mma (M = 128, N = NT, K = 16) per unit, A from tensor
+//                     its packed words from shared memory, rebuilds fp16((q - zero) * scale) in registers and
+//                     writes them into its own tensor-memory lane with tcgen05.st (one packed int32 = 8 consecutive
+//                     k of one column, which is exactly what a lane of the A operand holds)
+//   MMA warp          one elected thread issues 8 (16) x tcgen05.mma (M = 128, N = NT, K = 16) per unit, A from tensor
 //                     memory, B from the swizzled shared-memory tile, and commits to mbarriers that recycle the
 //                     stages; the accumulator never leaves tensor memory until the tile is done
 //   epilogue          4 warps read the accumulator (tcgen05.ld), convert to fp16 and store; a warpgroup of its own
 //                     except for 33..64 rows, where dequant warpgroup 0 does it
 //
-// Configurations (Cfg<NT, PAIR>): NT <= 32 rows stream the weights once from HBM - one CTA per SM, 4 dequant warpgroups,
-// 16 weight stages, 6 A / activation stages, and the (tile, unit) space cut into equal ranges per CTA (split-K over
-// the whole GPU, partial tiles summed through scratch in a fixed order).  NT = 64: two CTAs per SM, whole tiles.
+// Configurations (Cfg<NT, PAIR>): NT <= 32 rows stream the weights once from HBM - one CTA per SM, 3 dequant warpgroups,
+// 9 weight stages and 3 A / activation stages of 256 k, and the (tile, unit) space cut into equal ranges per CTA
+// (split-K over the whole GPU, partial tiles summed through scratch in a fixed order).  NT = 64: two CTAs per SM, whole tiles.
 // NT >= 128: one CTA per SM, whole tiles, epilogue stores transposed through shared memory; by default launched as
 // clusters of two CTAs that run each MMA together (cta_group::2, M = 256 over two SMs), see PAIR below.
 // Every wait is bounded and reports through the status word instead of hanging.
@@ -30,6 +31,7 @@
 #include <dlfcn.h>
 
 #include <atomic>
+#include <mutex>
 
 #include "common.cuh"
 #include "ptx.cuh"
@@ -56,6 +58,7 @@ struct UmmaParams {
     int CT;              // column tiles: ceil(S / 128)
     int MTILES;          // row tiles: ceil(rows / NT)
     int accumulate;
+    int overlap;         // host side only: launch with programmatic stream serialization (see launch_nt)
     int kparts;          // > 1: every tile's K range is cut into this many parts, one CTA (pair) each, fp32 partial outputs
                          // go to the scratch as (part, row, S) and kparts_reduce_kernel sums them (more than 32 rows only)
     GroupDiv gdiv;
@@ -109,15 +112,34 @@ __device__ __forceinline__ uint4 sparse_lut_entry(int mn) {
     return make_uint4(sel | ((4 * rank) << 16), pm[0], pm[1], 0);
 }
 
-// ---- formats: one 64-k unit of one column -> 32 registers of fp16 pairs in natural k order -------------------
-template <int BITS, bool SPARSE>
+// ---- formats: one 64-k part of one column -> 32 registers of fp16 pairs -----------------------------------------
+// The pairs are in natural k order, except for dense int4 with PERM: there register 4r + j of packed word r holds
+// (k_j, k_{j+4}) of the word's eight k, which needs no byte shuffles; the activation tile is permuted to match
+// (kPermutedK: position 2j + i of every group of eight k holds k_{j + 4i}).
+template <int BITS, bool SPARSE, bool PERM = false>
 struct UFormat;
 
-template <>
-struct UFormat<4, false> {
-    static constexpr int WROWS = 8, MROWS = 0;       // packed rows / mask rows per 64-k unit
+template <bool PERM>
+struct UFormat<4, false, PERM> {
+    static constexpr int WROWS = 8, MROWS = 0;       // packed rows / mask rows per 64-k part
+    static constexpr bool kPermutedK = PERM;
     template <int MODE>
     __device__ static __forceinline__ void decode(uint32_t wbase, uint32_t, const ColK& c, uint32_t (&A)[32], const uint4*) {
+        if (PERM) {
+            // nibbles j and j + 4 of a word sit at the same offset of its two 16-bit halves: one LOP3 per pair plants both
+            // into the mantissas of (1024, 1024); the odd nibbles come out multiplied by 16
+            const uint32_t off1 = hsub2_u(BASE_1_1, c.z2), off16 = hsub2_u(H2_N64, c.z2);
+#pragma unroll
+            for (int r = 0; r < 8; ++r) {
+                const uint32_t w = ptx::lds32(wbase + r * 512);
+                const uint32_t w8 = w >> 8;
+                A[4 * r + 0] = finish<4, MODE>(and_or(w, 0x000F000Fu, kMagic1024), MUL_1_1, BASE_1_1, off1, c);      // k0, k4
+                A[4 * r + 1] = finish<4, MODE>(and_or(w, 0x00F000F0u, kMagic1024), H2_1_16, H2_N64, off16, c);       // k1, k5
+                A[4 * r + 2] = finish<4, MODE>(and_or(w8, 0x000F000Fu, kMagic1024), MUL_1_1, BASE_1_1, off1, c);     // k2, k6
+                A[4 * r + 3] = finish<4, MODE>(and_or(w8, 0x00F000F0u, kMagic1024), H2_1_16, H2_N64, off16, c);      // k3, k7
+            }
+            return;
+        }
         const uint32_t off = hsub2_u(BASE_1_16, c.z2);
 #pragma unroll
         for (int r = 0; r < 8; ++r) {
@@ -131,9 +153,10 @@ struct UFormat<4, false> {
     }
 };
 
-template <>
-struct UFormat<2, false> {
+template <bool PERM>
+struct UFormat<2, false, PERM> {
     static constexpr int WROWS = 4, MROWS = 0;
+    static constexpr bool kPermutedK = false;
     template <int MODE>
     __device__ static __forceinline__ void decode(uint32_t wbase, uint32_t, const ColK& c, uint32_t (&A)[32], const uint4*) {
         const uint32_t offa = hsub2_u(BASE_1_4, c.z2), offb = hsub2_u(BASE_16_64, c.z2);
@@ -153,9 +176,10 @@ struct UFormat<2, false> {
     }
 };
 
-template <>
-struct UFormat<3, false> {
+template <bool PERM>
+struct UFormat<3, false, PERM> {
     static constexpr int WROWS = 6, MROWS = 0;
+    static constexpr bool kPermutedK = false;
     template <int MODE>
     __device__ static __forceinline__ void decode(uint32_t wbase, uint32_t, const ColK& c, uint32_t (&A)[32], const uint4*) {
         const uint32_t off = hsub2_u(BASE_1_8, c.z2);
@@ -183,9 +207,10 @@ struct UFormat<3, false> {
     }
 };
 
-template <>
-struct UFormat<4, true> {
+template <bool PERM>
+struct UFormat<4, true, PERM> {
     static constexpr int WROWS = 4, MROWS = 2;
+    static constexpr bool kPermutedK = false;
     template <int MODE>
     __device__ static __forceinline__ void decode(uint32_t wbase, uint32_t mbase, const ColK& c, uint32_t (&A)[32], const uint4* lut) {
         const uint32_t off = hsub2_u(BASE_1_1, c.z2);
@@ -213,13 +238,13 @@ struct UFormat<4, true> {
     }
 };
 
-template <class F>
-struct WStage {     // one stage of the packed-weight ring: 128 k = two 64-k halves
-    static constexpr int kW = 0;                                 // 2 * WROWS packed rows of 512 B
-    static constexpr int kMask = 2 * F::WROWS * 512;             // 2 * MROWS mask rows of 512 B
-    static constexpr int kS = kMask + 2 * F::MROWS * 512;        // 2 rows of scales (group g0, g0 + 1), 256 B each
-    static constexpr int kZ = kS + 512;                          // 2 rows of zeros
-    static constexpr int kBytes = kZ + 512;
+template <class F, int H>
+struct WStage {     // one stage of the packed-weight ring: one unit = H parts of 64 k
+    static constexpr int kW = 0;                                 // H * WROWS packed rows of 512 B
+    static constexpr int kMask = H * F::WROWS * 512;             // H * MROWS mask rows of 512 B
+    static constexpr int kS = kMask + H * F::MROWS * 512;        // H rows of scales (groups g0 .. g0 + H - 1), 256 B each
+    static constexpr int kZ = kS + H * 256;                      // H rows of zeros
+    static constexpr int kBytes = kZ + H * 256;
 };
 
 constexpr int kMaxWStages = 16;
@@ -240,23 +265,32 @@ struct Cfg {
     // not landed yet (tensor-map copies may complete out of order) and take the stale phase for its own: there the
     // dequant warps first wait, like the producer, until the previous use has been released (kWGuard).  And there
     // are at least as many A stages as warpgroups (checked in the kernel).
-    static constexpr int kWStages = kStream ? 16 : NT <= 64 ? 8 : kDequantBound ? 6 : 3;
-    static constexpr int kWG = (kStream || kDequantBound) ? 4 : 2;    // dequant warpgroups (4 warps each), taking units in turn
-    static constexpr int kABStages = kStream ? 6 : NT == 128 ? 4 : 3;   // ring of (A in tensor memory, activation tile in shared memory) pairs, 128 k per stage
+    // A unit (one stage of every ring) is kHalves parts of 64 k.  The producers and the MMA issuer are single threads
+    // whose loops cost ~500 cycles per stage whatever its size (an mbarrier wait ~190 cycles even when it is already
+    // complete, expect_tx + the copy's issue another ~190): at 128 k per stage that alone is ~27 us for 16384 x 16384
+    // weights on 148 SMs, so the weight-streaming shapes use 256-k units.
+    static constexpr int kHalves = kStream ? 4 : 2;
+    static constexpr int kWStages = kStream ? 9 : NT <= 64 ? 8 : kDequantBound ? 6 : 3;
+    static constexpr int kWG = kStream ? 3 : kDequantBound ? 4 : 2;   // dequant warpgroups (4 warps each), taking units in turn
+    static constexpr int kABStages = kStream ? 3 : NT == 128 ? 4 : 3;   // ring of (A in tensor memory, activation tile in shared memory) pairs, one unit per stage
     static constexpr bool kWGuard = kWStages % kWG != 0;
     static constexpr bool kEpiWarps = NT >= 128 || kStream;           // a warpgroup of its own for the epilogue (else dequant warpgroup 0 does it)
     static constexpr bool kEpiTransposed = NT >= 128;                 // epilogue stores go through a shared-memory transposition tile
     static constexpr bool kEpiHandoff = kStream;                      // the MMA warp waits for the accumulator and wakes the epilogue warps (named barrier)
     static constexpr bool kDeferArrive = kStream;                     // a dequant warp announces an A stage only before its next wait (hides the tcgen05.wait::st latency)
-    static constexpr bool kSZProducer = kStream;                      // scales / zeros are issued by a thread of their own
     // many rows: two epilogue warpgroups, each draining half of the accumulator's columns, so that the next tile's
     // MMAs wait half as long for the accumulator
     static constexpr int kEpiGroups = NT >= 128 ? 2 : 1;
-    static constexpr int kWarps = 4 * kWG + (kEpiWarps ? 4 * kEpiGroups : 0) + 3 + (kSZProducer ? 1 : 0);  // + weight producer, activation producer, MMA issuer
+    // The weight-streaming shapes have two weight-producer threads (in two warps) that fill the stages in turn: one
+    // thread's loop (wait ~190 cycles, expect_tx + copies ~250) delivers a 16 KB stage per ~500-700 cycles, about
+    // 4-5 TB/s over the whole GPU, which is less than the memory system can stream.
+    static constexpr int kWProducers = kStream ? 2 : 1;
+    static constexpr int kWarps = 4 * kWG + (kEpiWarps ? 4 * kEpiGroups : 0) + 3 + (kWProducers - 1);  // + weight producer(s), activation producer, MMA issuer
     static constexpr int kThreads = kWarps * 32;
     static constexpr int kDCols = NT < 32 ? 32 : NT;                  // accumulator columns
-    static constexpr int kACol0 = kDCols;                             // A stages follow: 64 columns (128 k) each
-    static constexpr int kColsUsed = kDCols + 64 * kABStages;
+    static constexpr int kACol0 = kDCols;                             // A stages follow: 32 columns per 64 k
+    static constexpr int kAStageCols = 32 * kHalves;
+    static constexpr int kColsUsed = kDCols + kAStageCols * kABStages;
     static constexpr int kTmemCols = kColsUsed <= 256 ? 256 : 512;
     // split-K over CTAs with a scratch reduction.  The code handles tiles of up to 128 rows, but the reducing CTA reads
     // its partners' partial tiles in dependent L2 round trips (rows x partners / 8 of them): measured at 128 rows that
@@ -270,13 +304,14 @@ struct Cfg {
 // many stages as tensor memory has columns for (accumulator + 64 per stage <= 512).
 template <int NT, bool PAIR>
 struct ABStages {
-    static constexpr int value = !PAIR ? Cfg<NT, false>::kABStages : (Cfg<NT, true>::kDCols + 64 * 5 <= 512 ? 5 : 4);
+    static constexpr int value = !PAIR ? Cfg<NT, false>::kABStages : (Cfg<NT, true>::kDCols + 64 * 5 <= 512 ? 5 : 4);   // pairs: 128-k units
 };
 
 struct Barriers {
     unsigned long long w_full[kMaxWStages], w_empty[kMaxWStages];
     unsigned long long ab_full[kMaxABStages];  // 4 dequant warps + the activation producer (with its transaction bytes)
     unsigned long long ab_free[kMaxABStages];  // tcgen05.commit: the MMAs that read the stage are done
+    unsigned long long b_landed[kMaxABStages]; // permuted k order only: the activation tile's copy has arrived (the producer warp then reorders it)
     unsigned long long d_full, d_empty;
 };
 
@@ -292,10 +327,11 @@ __device__ __forceinline__ int range_owner(long long T, long long G, long long t
 }
 
 struct TensorMaps {
-    CUtensorMap x;   // fp16 (rows, N):        box 64 k x NT rows, 128-byte swizzle
-    CUtensorMap w;   // int32 (R, S):          box 128 columns x 2 * WROWS rows
-    CUtensorMap m;   // int32 (N / 32, S):     box 128 columns x 2 * MROWS rows (sparse format only)
-    CUtensorMap s;   // fp16 (n_groups, S):    box 128 columns x 2 rows
+    CUtensorMap x;   // fp16 (rows, N):        box 64 k x NT rows, 128-byte swizzle; weight-streaming shapes: seen as
+                     //                        (N / 64, rows, 64) with box kHalves x NT x 64, one copy per unit
+    CUtensorMap w;   // int32 (R, S):          box 128 columns x kHalves * WROWS rows
+    CUtensorMap m;   // int32 (N / 32, S):     box 128 columns x kHalves * MROWS rows (sparse format only)
+    CUtensorMap s;   // fp16 (n_groups, S):    box 128 columns x kHalves rows
     CUtensorMap z;
 };
 
@@ -305,19 +341,20 @@ struct TensorMaps {
 template <int BITS, bool SPARSE, int NT, bool PAIR>
 __global__ void __launch_bounds__(Cfg<NT, PAIR>::kThreads, Cfg<NT, PAIR>::kMinBlocks)
 umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
-    using F = UFormat<BITS, SPARSE>;
-    using WS = WStage<F>;
     using C = Cfg<NT, PAIR>;
+    using F = UFormat<BITS, SPARSE, C::kStream>;                     // weight-streaming shapes: the cheaper k order where the format has one
+    constexpr int H = C::kHalves;                                    // 64-k parts per unit
+    using WS = WStage<F, H>;
     static_assert(!PAIR || (NT >= 128 && !C::kEpiHandoff), "CTA pairs are for the many-row shapes");
     static_assert((2 * C::kWStages) % C::kWG == 0, "every second use of a weight stage must be by the same warpgroup");
     static_assert(ABStages<NT, PAIR>::value >= C::kWG, "fewer A stages than warpgroups: a parity wait could see the phase before last");
     constexpr int kBHalfBytes = (PAIR ? NT / 2 : NT) * 128;        // one 64-k activation sub-tile held by this CTA
-    constexpr int kBStageBytes = 2 * kBHalfBytes;
+    constexpr int kBStageBytes = H * kBHalfBytes;
     // single CTAs at NT = 256 have no shared memory left for a second transposition tile: the second epilogue group idles
     constexpr int kEpiGroups = (C::kEpiGroups == 2 && (PAIR || NT < 256)) ? 2 : 1;
     constexpr int kEpiWarp0 = 4 * C::kWG;                           // first epilogue warp (a multiple of 4: lane quarter = warp % 4)
     constexpr int kWProducer = kEpiWarp0 + (C::kEpiWarps ? 4 * C::kEpiGroups : 0), kBProducer = kWProducer + 1, kMma = kWProducer + 2;
-    constexpr int kSZWarp = kWProducer + 3;                         // only when Cfg::kSZProducer
+    constexpr int kWProducer2 = kWProducer + 3;                     // only when Cfg::kWProducers == 2
     constexpr int kABStages = ABStages<NT, PAIR>::value;
     extern __shared__ __align__(1024) unsigned char smem[];      // [B ring (1024-aligned tiles)][W ring]
     __shared__ __align__(8) Barriers bars;
@@ -344,7 +381,7 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
             if (SPARSE) ptx::prefetch_tmap(&tm.m);
         }
         if (lane < C::kWStages) {
-            ptx::mbar_init(ptx::smem_u32(&bars.w_full[lane]), C::kSZProducer ? 2 : 1);
+            ptx::mbar_init(ptx::smem_u32(&bars.w_full[lane]), 1);
             ptx::mbar_init(ptx::smem_u32(&bars.w_empty[lane]), 4);
         }
         ptx::fence_mbar_init();
@@ -357,6 +394,7 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
                 // a pair's stage is full when the dequant warps of both CTAs and both activation halves have arrived
                 ptx::mbar_init(ptx::smem_u32(&bars.ab_full[lane]), PAIR ? 4 + 4 + 1 : 4 + 1);
                 ptx::mbar_init(ptx::smem_u32(&bars.ab_free[lane]), 1);
+                ptx::mbar_init(ptx::smem_u32(&bars.b_landed[lane]), 1);
             }
             if (lane == 31) {
                 ptx::mbar_init(ptx::smem_u32(&bars.d_full), 1);
@@ -386,8 +424,11 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
         ptx::tc_fence_after_sync();
     }
     const uint32_t tmem_base = tmem_base_smem;       // not valid in the weight producer's warp, which never uses it
+    // The next kernel of the stream may be scheduled from here on (it takes an SM only when a CTA of this grid has left
+    // it); if it is one of these kernels, its set-up and its first weight copies then overlap this grid's tail.
+    if (threadIdx.x == 0) ptx::grid_launch_dependents();
 
-    // ---- this CTA's share of the (tile, unit) space; one unit = 128 k.  Whole tiles unless the split-K variant ----
+    // ---- this CTA's share of the (tile, unit) space; one unit = H x 64 k.  Whole tiles unless the split-K variant ----
     const long long U = p.U;
     const int CTd = PAIR ? (p.CT + 1) / 2 : p.CT;                  // column tiles of a CTA, or column-tile pairs of a CTA pair
     const long long n_tiles = (long long)p.MTILES * CTd;
@@ -412,11 +453,12 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
         t_hi = range_lo(n_tiles, G, b + 1) * U;
     }
 
-    if (warp == kWProducer) {
-        // =========================== packed weights + scales / zeros: one thread ===========================
+    if (warp == kWProducer || (C::kWProducers == 2 && warp == kWProducer2)) {
+        // =========================== packed weights (+ scales / zeros): one thread per producer warp ===========================
         if (lane == 0) {
             // every box is copied whole (out-of-range parts are zero-filled)
-            constexpr uint32_t kBytes = (uint32_t)(C::kSZProducer ? WS::kS : WS::kBytes);
+            constexpr uint32_t kBytes = (uint32_t)WS::kBytes;
+            const uint32_t mine = warp == kWProducer ? 0u : 1u;             // with two producers: the stages of this parity
             uint32_t si = 0, ws = 0, wph = 0;
             bool ok = true;
             for (long long t = t_lo; t < t_hi && ok;) {
@@ -425,13 +467,13 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
                 const int u1 = (int)min(U, u0 + (t_hi - t));
                 const int ct = tile_ct(tile);
                 for (int u = u0; u < u1; ++u, ++si) {
-                    if (!ptx::mbar_wait_relaxed(ptx::smem_u32(&bars.w_empty[ws]), wph ^ 1u, 1600)) { atomicExch(p.status, 11); ok = false; break; }
-                    const uint32_t st = w_ring + ws * WS::kBytes, full = ptx::smem_u32(&bars.w_full[ws]);
-                    ptx::mbar_arrive_expect_tx(full, kBytes);
-                    ptx::tma_load_2d(st + WS::kW, &tm.w, ct * 128, u * 2 * F::WROWS, full);
-                    if (SPARSE) ptx::tma_load_2d(st + WS::kMask, &tm.m, ct * 128, u * 2 * F::MROWS, full);
-                    if (!C::kSZProducer) {
-                        const int g0 = (int)p.gdiv(2u * (uint32_t)u);
+                    if (C::kWProducers == 1 || (si & 1u) == mine) {
+                        if (!ptx::mbar_wait(ptx::smem_u32(&bars.w_empty[ws]), wph ^ 1u)) { atomicExch(p.status, 11); ok = false; break; }
+                        const uint32_t st = w_ring + ws * WS::kBytes, full = ptx::smem_u32(&bars.w_full[ws]);
+                        ptx::mbar_arrive_expect_tx(full, kBytes);
+                        ptx::tma_load_2d(st + WS::kW, &tm.w, ct * 128, u * H * F::WROWS, full);
+                        if (SPARSE) ptx::tma_load_2d(st + WS::kMask, &tm.m, ct * 128, u * H * F::MROWS, full);
+                        const int g0 = (int)p.gdiv((uint32_t)H * (uint32_t)u);
                         ptx::tma_load_2d(st + WS::kS, &tm.s, ct * 128, g0, full);
                         ptx::tma_load_2d(st + WS::kZ, &tm.z, ct * 128, g0, full);
                     }
@@ -440,41 +482,77 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
                 t += u1 - u0;
             }
         }
-    } else if (C::kSZProducer && warp == kSZWarp) {
-        // =========================== scales / zeros of the weight stages: one thread ===========================
-        if (lane == 0) {
-            uint32_t ws = 0, wph = 0;
-            bool ok = true;
-            for (long long t = t_lo; t < t_hi && ok;) {
-                const long long tile = div_nn(t, U);
-                const int u0 = (int)(t - tile * U);
-                const int u1 = (int)min(U, u0 + (t_hi - t));
-                const int ct = tile_ct(tile);
-                for (int u = u0; u < u1; ++u) {
-                    if (!ptx::mbar_wait_relaxed(ptx::smem_u32(&bars.w_empty[ws]), wph ^ 1u, 1600)) { atomicExch(p.status, 13); ok = false; break; }
-                    const uint32_t st = w_ring + ws * WS::kBytes, full = ptx::smem_u32(&bars.w_full[ws]);
-                    ptx::mbar_arrive_expect_tx(full, (uint32_t)(WS::kBytes - WS::kS));
-                    const int g0 = (int)p.gdiv(2u * (uint32_t)u);
-                    ptx::tma_load_2d(st + WS::kS, &tm.s, ct * 128, g0, full);
-                    ptx::tma_load_2d(st + WS::kZ, &tm.z, ct * 128, g0, full);
-                    if (++ws == C::kWStages) { ws = 0; wph ^= 1u; }
+    } else if (warp == kBProducer && C::kStream && F::kPermutedK) {
+        // =========================== activation tiles in the permuted k order: the whole warp ===========================
+        // Lane 0 keeps up to kABStages copies in flight (one 3-D copy per unit, natural k order); when a tile has landed,
+        // the warp reorders every 16-byte chunk (eight consecutive k) of its valid rows in place to
+        // (k0, k4, k1, k5, k2, k6, k3, k7), the order the dequant warps produce without byte shuffles, and only then
+        // announces the stage to the MMA warp.  A chunk stays where it is, so the 128-byte swizzle does not matter here.
+        ptx::grid_dependency_wait();      // the activations may be the output of the kernel before this one in the stream
+        const int total = (int)(t_hi - t_lo);
+        int issued = 0;
+        bool ok = true;
+        for (int i = 0; i < total && ok; ++i) {
+            while (issued < total && issued < i + kABStages) {
+                const uint32_t s = (uint32_t)(issued % kABStages), ph = (uint32_t)(issued / kABStages) & 1u;
+                const uint32_t free_bar = ptx::smem_u32(&bars.ab_free[s]);
+                if (issued > i) {
+                    // look-ahead only while the stage is free: never wait for it with a landed tile still to reorder
+                    if (!ptx::mbar_test_wait(free_bar, ph ^ 1u)) break;
+                } else if (!ptx::mbar_wait(free_bar, ph ^ 1u)) {
+                    if (lane == 0) atomicExch(p.status, 12);
+                    ok = false;
+                    break;
                 }
-                t += u1 - u0;
+                if (lane == 0) {
+                    const long long t = t_lo + issued;
+                    const long long tile = div_nn(t, U);
+                    const int u = (int)(t - tile * U);
+                    const uint32_t landed = ptx::smem_u32(&bars.b_landed[s]);
+                    ptx::mbar_arrive_expect_tx(landed, (uint32_t)kBStageBytes);
+                    ptx::tma_load_3d(b_ring + s * kBStageBytes, &tm.x, 0, tile_mt(tile) * NT, u * H, landed);
+                }
+                ++issued;
             }
+            if (!ok) break;
+            const uint32_t s = (uint32_t)(i % kABStages), ph = (uint32_t)(i / kABStages) & 1u;
+            if (!ptx::mbar_wait(ptx::smem_u32(&bars.b_landed[s]), ph)) {
+                if (lane == 0) atomicExch(p.status, 14);
+                break;
+            }
+            const int mt = tile_mt(div_nn(t_lo + i, U));
+            const int nrows = min(NT, p.rows - mt * NT);
+            // chunk index = row * (8 * H) + part * 8 + chunk of the 128-byte row segment
+            for (int idx = lane; idx < nrows * 8 * H; idx += 32) {
+                const int r = idx / (8 * H), hc = idx % (8 * H);
+                const uint32_t addr = b_ring + s * kBStageBytes + (hc >> 3) * kBHalfBytes + r * 128 + (hc & 7) * 16;
+                const uint4 a = ptx::lds128(addr);
+                uint4 o;
+                o.x = prmt(a.x, a.z, 0x5410);      // (k0, k4)
+                o.y = prmt(a.x, a.z, 0x7632);      // (k1, k5)
+                o.z = prmt(a.y, a.w, 0x5410);      // (k2, k6)
+                o.w = prmt(a.y, a.w, 0x7632);      // (k3, k7)
+                ptx::sts128(addr, o);
+            }
+            ptx::fence_proxy_async_smem();         // the MMAs read the tile through the async proxy
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&bars.ab_full[s]));
         }
     } else if (warp == kBProducer) {
-        // =========================== activation tiles, two 64-k sub-tiles per unit: one thread ===========================
+        // =========================== activation tiles, one 64-k sub-tile per part of a unit: one thread ===========================
         if (lane == 0) {
             uint32_t s = 0, ph = 0;
             bool ok = true;
+            // the activations may be the output of the kernel before this one in the stream (the weight-side tensors
+            // are not: see the launch attribute in launch_nt)
+            ptx::grid_dependency_wait();
             for (long long t = t_lo; t < t_hi && ok;) {
                 const long long tile = div_nn(t, U);
                 const int u0 = (int)(t - tile * U);
                 const int u1 = (int)min(U, u0 + (t_hi - t));
                 const int mt = tile_mt(tile);
                 for (int u = u0; u < u1; ++u) {
-                    if (!(C::kStream ? ptx::mbar_wait_relaxed(ptx::smem_u32(&bars.ab_free[s]), ph ^ 1u, 400)
-                                     : ptx::mbar_wait(ptx::smem_u32(&bars.ab_free[s]), ph ^ 1u))) { atomicExch(p.status, 12); ok = false; break; }
+                    if (!ptx::mbar_wait(ptx::smem_u32(&bars.ab_free[s]), ph ^ 1u)) { atomicExch(p.status, 12); ok = false; break; }
                     const uint32_t full = ptx::smem_u32(&bars.ab_full[s]);
                     if (PAIR) {
                         // both CTAs' halves are counted on the leader's barrier, which expects the bytes of both
@@ -483,6 +561,10 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
                         const int r0 = mt * NT + (int)rank * (NT / 2);
                         ptx::tma_load_2d_pair(b_ring + s * kBStageBytes, &tm.x, u * 128, r0, lfull);
                         ptx::tma_load_2d_pair(b_ring + s * kBStageBytes + kBHalfBytes, &tm.x, u * 128 + 64, r0, lfull);
+                    } else if (C::kStream) {
+                        // one copy per unit: H sub-tiles of 64 k, laid out one after the other
+                        ptx::mbar_arrive_expect_tx(full, (uint32_t)kBStageBytes);
+                        ptx::tma_load_3d(b_ring + s * kBStageBytes, &tm.x, 0, mt * NT, u * H, full);
                     } else {
                         ptx::mbar_arrive_expect_tx(full, (uint32_t)kBStageBytes);
                         ptx::tma_load_2d(b_ring + s * kBStageBytes, &tm.x, u * 128, mt * NT, full);
@@ -519,10 +601,10 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
                     }
                     ptx::tc_fence_after_sync();
                     const uint64_t bdesc = ptx::smem_desc_sw128(b_ring + s * kBStageBytes);
-                    const uint32_t a0 = tmem_base + C::kACol0 + s * 64;
+                    const uint32_t a0 = tmem_base + C::kACol0 + s * C::kAStageCols;
                     if (ptx::elect_one()) {
 #pragma unroll
-                        for (int k = 0; k < 8; ++k) {
+                        for (int k = 0; k < 4 * H; ++k) {
                             // K = 16 per instruction: +8 columns of A; B: +32 bytes (2 descriptor units) inside a 64-k sub-tile
                             const uint64_t bd = bdesc + (uint64_t)((k >> 2) * (kBHalfBytes >> 4) + (k & 3) * 2);
                             if (PAIR) ptx::umma_f16_ts_pair(tmem_base, a0 + k * 8, bd, idesc, (u > u0 || k > 0) ? 1u : 0u);
@@ -571,7 +653,13 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
         // =========================== dequant warpgroups; epilogue warps ===========================
         // Accumulator of one finished segment -> fp16 rows of `out`, or a partial tile for the split-K reduction.
         // Run by 4 warps whose index modulo 4 selects the 32 tensor-memory lanes (= weight columns) they may read.
+        bool dependency_waited = false;
         auto epilogue = [&](uint32_t seg, long long tile, int u0, int u1) -> bool {
+            if (!dependency_waited) {
+                // outputs, old outputs and the scratch may still be in use by the kernel before this one in the stream
+                ptx::grid_dependency_wait();
+                dependency_waited = true;
+            }
             const int mt = tile_mt(tile), ct = tile_ct(tile);
             const int col = (warp & 3) * 32 + lane;
             const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
@@ -659,6 +747,15 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
                     }
                 }
             };
+            // matvec route with more than 64 rows (a batch of one-row products): the caller's old values of rows
+            // j0 .. of this lane's column are added to the unrounded sums, so that there is still one rounding
+            auto add_old_outs = [&](uint32_t (&v)[16], int j0) {
+                if (!col_ok) return;
+#pragma unroll
+                for (int j = 0; j < 16; ++j)
+                    if (j0 + j < nrows)
+                        v[j] = __float_as_uint(__uint_as_float(v[j]) + __half2float(p.out[(size_t)(row0 + j0 + j) * p.S + scol]));
+            };
             if (C::kEpiTransposed) {
                 // 16 accumulator columns (= 16 output rows) at a time: transposed through a 4 KB shared-memory tile so that
                 // the global stores are 16-byte rows instead of one 2-byte element per lane
@@ -694,14 +791,11 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
                             put_kpart(v, j0);
                             continue;
                         }
+                        if (p.accumulate) add_old_outs(v, j0);
 #pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            float f = __uint_as_float(v[j]);
-                            // matvec route with many rows: add the caller's old value to the unrounded sum (one rounding)
-                            if (p.accumulate && col_ok && j0 + j < nrows)
-                                f += __half2float(p.out[(size_t)(row0 + j0 + j) * p.S + scol]);
-                            ptx::sts16(stage + (j0 - eg * kShare + j) * 256 + col * 2, __half_as_ushort(__float2half_rn(f)));
-                        }
+                        for (int j = 0; j < 16; ++j)
+                            ptx::sts16(stage + (j0 - eg * kShare + j) * 256 + col * 2,
+                                       __half_as_ushort(__float2half_rn(__uint_as_float(v[j]))));
                     }
                     ptx::named_bar_sync(bar_id, 128);
 #pragma unroll 1
@@ -738,13 +832,10 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
                         put_kpart(v, j0);
                         continue;
                     }
+                    if (p.accumulate) add_old_outs(v, j0);
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        float f = __uint_as_float(v[j]);
-                        if (p.accumulate && col_ok && j0 + j < nrows)
-                            f += __half2float(p.out[(size_t)(row0 + j0 + j) * p.S + scol]);
-                        ptx::sts16(stage_tile + j * 256 + col * 2, __half_as_ushort(__float2half_rn(f)));
-                    }
+                    for (int j = 0; j < 16; ++j)
+                        ptx::sts16(stage_tile + j * 256 + col * 2, __half_as_ushort(__float2half_rn(__uint_as_float(v[j]))));
                     ptx::named_bar_sync(bar_id, 128);
 #pragma unroll
                     for (int r = 0; r < 2; ++r) {
@@ -846,52 +937,98 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
                         break;
                     }
                     const uint32_t st = w_ring + ws * WS::kBytes;
-                    const uint32_t g0 = p.gdiv(2u * (uint32_t)u);
+                    const uint32_t g0 = p.gdiv((uint32_t)H * (uint32_t)u);
                     const uint32_t as = si % kABStages, aph = (si / kABStages) & 1u;
-                    // polled before the first half is decoded, so that the answer costs no latency when it is needed
+                    // polled before the first part is decoded, so that the answer costs no latency when it is needed
                     const bool free_early = ptx::mbar_test_wait(ptx::smem_u32(&bars.ab_free[as]), aph ^ 1u);
-#pragma unroll
-                    for (int h = 0; h < 2; ++h) {
-                        ColK c;
-                        {
-                            const uint32_t row = (h == 0) ? 0u : (p.gdiv(2u * (uint32_t)u + 1u) - g0);   // 0 or 1
-                            const uint32_t sz = ptx::lds32(st + WS::kS + row * 256 + (col & ~1) * 2) >> (16 * (col & 1));
-                            const uint32_t zz = ptx::lds32(st + WS::kZ + row * 256 + (col & ~1) * 2) >> (16 * (col & 1));
-                            c.s2 = prmt(sz, sz, 0x1010);
-                            c.z2 = prmt(zz, zz, 0x1010);
-                        }
-                        // fast mode needs: scale sign clear, zero-point an integer in [0, 512] ([0, 255] for the sparse format)
+                    // scale and zero-point of this thread's column in row `row` of the stage's group box, both halves of a register
+                    auto load_group = [&](uint32_t row, ColK& c) {
+                        const uint32_t sz = ptx::lds32(st + WS::kS + row * 256 + (col & ~1) * 2) >> (16 * (col & 1));
+                        const uint32_t zz = ptx::lds32(st + WS::kZ + row * 256 + (col & ~1) * 2) >> (16 * (col & 1));
+                        c.s2 = prmt(sz, sz, 0x1010);
+                        c.z2 = prmt(zz, zz, 0x1010);
+                        c.zb = 0;
+                    };
+                    // fast mode needs: scale sign clear, zero-point an integer in [0, 512] ([0, 255] for the sparse format)
+                    auto not_fast_bits = [&](const ColK& c) -> uint32_t {
                         const uint32_t zr = hadd2_u(hadd2_u(c.z2, kMagic1024), H2_N1024);
                         constexpr uint32_t kAdd = SPARSE ? 0x2407u : 0x1FFFu;
                         const uint32_t zlo = c.z2 & 0xFFFFu;
-                        const uint32_t not_fast = ((zlo | ((zlo & 0x7FFFu) + kAdd) | c.s2) & 0x8000u) | (zr ^ c.z2);
-                        const uint32_t wb = st + WS::kW + h * (F::WROWS * 512) + col * 4;
-                        const uint32_t mb = st + WS::kMask + h * (F::MROWS * 512) + col * 4;
-                        uint32_t A[32];
-                        if (!__any_sync(0xFFFFFFFFu, not_fast != 0)) {
-                            if (SPARSE) c.zb = __half2uint_rz(__ushort_as_half((unsigned short)zlo)) * 0x01010101u;
-                            F::template decode<MODE_FAST>(wb, mb, c, A, lut);
-                        } else {
-                            c.zb = 0;
-                            const bool lin = __hge(__ushort_as_half((unsigned short)(c.s2 & 0xFFFFu)), __ushort_as_half(0));
-                            if (__all_sync(0xFFFFFFFFu, lin)) F::template decode<MODE_GENERAL>(wb, mb, c, A, lut);
-                            else F::template decode<MODE_SLOW>(wb, mb, c, A, lut);
+                        return ((zlo | ((zlo & 0x7FFFu) + kAdd) | c.s2) & 0x8000u) | (zr ^ c.z2);
+                    };
+                    // after the last read of the weight stage
+                    auto release_weights = [&]() {
+                        __syncwarp();
+                        if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&bars.w_empty[ws]));
+                    };
+                    // before the first store into the A stage
+                    auto acquire_a_stage = [&]() -> bool {
+                        if (C::kDeferArrive && pending >= 0) announce(pending);       // before any wait: the MMAs must be able to go on
+                        // the A stage (and its activation tile) is free once the MMAs of its previous use have completed
+                        if (!free_early && !ptx::mbar_wait(ptx::smem_u32(&bars.ab_free[as]), aph ^ 1u)) {
+                            if (lane == 0) atomicExch(p.status, 32);
+                            return false;
                         }
-                        if (h == 1) {
-                            __syncwarp();
-                            if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&bars.w_empty[ws]));   // both halves are in registers now
-                        }
-                        if (h == 0) {
-                            if (C::kDeferArrive && pending >= 0) announce(pending);       // before any wait: the MMAs must be able to go on
-                            // the A stage (and its activation tile) is free once the MMAs of its previous use have completed
-                            if (!free_early && !ptx::mbar_wait(ptx::smem_u32(&bars.ab_free[as]), aph ^ 1u)) {
-                                if (lane == 0) atomicExch(p.status, 32);
-                                ok = false;
+                        ptx::tc_fence_after_sync();
+                        return true;
+                    };
+                    // The parts are decoded in the fast mode by straight-line code, without a mode decision in between;
+                    // whether every group of the unit really is in the fast mode (for every column of the warp) is
+                    // voted once, when the last group has been read and before the weight stage is released.  If not,
+                    // the unit is decoded again with a decision per part (the stores are simply overwritten).
+                    bool redo = false;
+                    {
+                        ColK c;
+                        uint32_t cur_row = 0xFFFFFFFFu, nf = 0;
+#pragma unroll
+                        for (int h = 0; h < H; ++h) {
+                            // scale and zero-point change only where the group does (warp-uniform)
+                            const uint32_t row = (h == 0) ? 0u : (p.gdiv((uint32_t)H * (uint32_t)u + (uint32_t)h) - g0);   // 0 .. H - 1
+                            if (row != cur_row) {
+                                cur_row = row;
+                                load_group(row, c);
+                                nf |= not_fast_bits(c);
+                                if (SPARSE) c.zb = __half2uint_rz(__ushort_as_half((unsigned short)(c.z2 & 0xFFFFu))) * 0x01010101u;
+                            }
+                            if (h == H - 1 && __any_sync(0xFFFFFFFFu, nf != 0)) {
+                                redo = true;
                                 break;
                             }
-                            ptx::tc_fence_after_sync();
+                            uint32_t A[32];
+                            F::template decode<MODE_FAST>(st + WS::kW + h * (F::WROWS * 512) + col * 4, st + WS::kMask + h * (F::MROWS * 512) + col * 4, c, A, lut);
+                            if (h == H - 1) release_weights();
+                            if (h == 0 && !acquire_a_stage()) { ok = false; break; }
+                            ptx::tmem_st32(lane_addr + C::kACol0 + as * C::kAStageCols + h * 32, A);
                         }
-                        ptx::tmem_st32(lane_addr + C::kACol0 + as * 64 + h * 32, A);
+                    }
+                    if (redo && ok) {
+                        // some group needs the general or the per-weight mode (rolled loop: three decode bodies in the
+                        // instruction cache, not three per part)
+                        ptx::tc_wait_st();
+                        ColK c;
+                        uint32_t cur_row = 0xFFFFFFFFu;
+#pragma unroll 1
+                        for (int h = 0; h < H; ++h) {
+                            const uint32_t row = (h == 0) ? 0u : (p.gdiv((uint32_t)H * (uint32_t)u + (uint32_t)h) - g0);
+                            if (row != cur_row) {
+                                cur_row = row;
+                                load_group(row, c);
+                            }
+                            const uint32_t wb = st + WS::kW + h * (F::WROWS * 512) + col * 4;
+                            const uint32_t mb = st + WS::kMask + h * (F::MROWS * 512) + col * 4;
+                            uint32_t A[32];
+                            if (!__any_sync(0xFFFFFFFFu, not_fast_bits(c) != 0)) {
+                                if (SPARSE) c.zb = __half2uint_rz(__ushort_as_half((unsigned short)(c.z2 & 0xFFFFu))) * 0x01010101u;
+                                F::template decode<MODE_FAST>(wb, mb, c, A, lut);
+                            } else {
+                                c.zb = 0;
+                                const bool lin = __hge(__ushort_as_half((unsigned short)(c.s2 & 0xFFFFu)), __ushort_as_half(0));
+                                if (__all_sync(0xFFFFFFFFu, lin)) F::template decode<MODE_GENERAL>(wb, mb, c, A, lut);
+                                else F::template decode<MODE_SLOW>(wb, mb, c, A, lut);
+                            }
+                            if (h == H - 1) release_weights();
+                            ptx::tmem_st32(lane_addr + C::kACol0 + as * C::kAStageCols + h * 32, A);
+                        }
                     }
                     if (!ok) break;
                     // (not deferred for the warpgroup's first stage: the pipeline is still filling and the MMA warp is waiting)
@@ -922,6 +1059,10 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
 // Sums the K parts written by umma_kernel (fp32, (part, row, S)) in part order, rounds once to fp16, and puts the
 // scratch back to all-zero (the split-K reduction of the few-row shapes relies on that).  8 columns per thread.
 __global__ void kparts_reduce_kernel(float* __restrict__ parts, __half* __restrict__ out, int rows, int S, int kparts) {
+    // (launched with programmatic stream serialization: the next kernel may be scheduled at once, this one touches
+    // nothing before the kernel that wrote the parts has completed)
+    ptx::grid_launch_dependents();
+    ptx::grid_dependency_wait();
     const long long n8 = (long long)rows * S / 8;
     const size_t stride = (size_t)rows * S;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (long long)gridDim.x * blockDim.x) {
@@ -982,6 +1123,79 @@ bool encode_2d(CUtensorMap* out, const void* base, CUtensorMapDataType dt, int e
 // what the last tcgen05 launch of this host thread chose: tile rows + 1000 if CTA pairs + 10000 * K parts (tests read it)
 thread_local int g_last_shape = 0;
 
+// Encoded tensor maps are a pure function of (base address, shape, box, swizzle): callers multiply with the same
+// weight tensors over and over, so the maps are kept in a small direct-mapped table instead of being encoded by the
+// driver five times per call (which costs more host time than the launch itself).
+struct MapKey {
+    const void* base;
+    uint64_t rows, cols;
+    uint32_t box_rows, box_cols;
+    int dt, elem_bytes, swz;
+    bool operator==(const MapKey& o) const {
+        return base == o.base && rows == o.rows && cols == o.cols && box_rows == o.box_rows && box_cols == o.box_cols &&
+               dt == o.dt && elem_bytes == o.elem_bytes && swz == o.swz;
+    }
+};
+struct MapSlot {
+    MapKey key;
+    CUtensorMap map;
+    bool valid;
+};
+constexpr int kMapSlots = 512;
+std::mutex g_map_mutex;
+MapSlot g_map_cache[kMapSlots];
+
+bool encode_2d_cached(CUtensorMap* out, const void* base, CUtensorMapDataType dt, int elem_bytes, uint64_t rows, uint64_t cols,
+                      uint32_t box_rows, uint32_t box_cols, CUtensorMapSwizzle swz) {
+    const MapKey key{base, rows, cols, box_rows, box_cols, (int)dt, elem_bytes, (int)swz};
+    uint64_t h = (uint64_t)(uintptr_t)base * 0x9E3779B97F4A7C15ull;
+    h ^= (rows * 0xC2B2AE3D27D4EB4Full) ^ (cols << 17) ^ ((uint64_t)box_rows << 40) ^ ((uint64_t)box_cols << 52) ^ (uint64_t)dt;
+    MapSlot& slot = g_map_cache[(h >> 32) % kMapSlots];
+    {
+        std::lock_guard<std::mutex> lock(g_map_mutex);
+        if (slot.valid && slot.key == key) {
+            *out = slot.map;
+            return true;
+        }
+    }
+    if (!encode_2d(out, base, dt, elem_bytes, rows, cols, box_rows, box_cols, swz)) return false;
+    std::lock_guard<std::mutex> lock(g_map_mutex);
+    slot.key = key;
+    slot.map = *out;
+    slot.valid = true;
+    return true;
+}
+
+// The activations (rows, N) of the weight-streaming shapes seen as (N / 64 blocks, rows, 64 k): one copy fetches the
+// `blocks` consecutive 64-k sub-tiles of a unit, each box_rows x 128 bytes in the 128-byte swizzle, one after the other.
+bool encode_x_blocks_cached(CUtensorMap* out, const void* base, uint64_t rows, uint64_t n, uint32_t box_rows, uint32_t blocks) {
+    const MapKey key{base, rows, n, box_rows, blocks, -3, 2, (int)CU_TENSOR_MAP_SWIZZLE_128B};
+    uint64_t h = (uint64_t)(uintptr_t)base * 0x9E3779B97F4A7C15ull;
+    h ^= (rows * 0xC2B2AE3D27D4EB4Full) ^ (n << 17) ^ ((uint64_t)box_rows << 40) ^ ((uint64_t)blocks << 52) ^ 0x33ull;
+    MapSlot& slot = g_map_cache[(h >> 32) % kMapSlots];
+    {
+        std::lock_guard<std::mutex> lock(g_map_mutex);
+        if (slot.valid && slot.key == key) {
+            *out = slot.map;
+            return true;
+        }
+    }
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc) return false;
+    const cuuint64_t dims[3] = {64, (cuuint64_t)rows, (cuuint64_t)(n / 64)};
+    const cuuint64_t strides[2] = {(cuuint64_t)n * 2, 128};
+    const cuuint32_t box[3] = {64, box_rows, blocks};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    if (enc(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return false;
+    std::lock_guard<std::mutex> lock(g_map_mutex);
+    slot.key = key;
+    slot.map = *out;
+    slot.valid = true;
+    return true;
+}
+
 constexpr long long kPartialWords = 148LL * 4 * 32 * 128;      // 64-bit words of partial tiles in the workspace (capi.cu sizes it)
 
 // More than 32 rows and tiles that fill less than half of the GPU: cut K into parts so that
@@ -999,10 +1213,18 @@ int launch_kparts_reduce(const UmmaParams& p, cudaStream_t stream, cudaError_t* 
     const long long n8 = (long long)p.rows * p.S / 8;
     long long blocks = (n8 + 255) / 256;
     if (blocks > 148 * 8) blocks = 148 * 8;
-    kparts_reduce_kernel<<<(int)blocks, 256, 0, stream>>>(p.partials, p.out, p.rows, p.S, p.kparts);
-    count_launch();
-    const cudaError_t e = cudaGetLastError();
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.gridDim = dim3((unsigned)blocks, 1, 1);
+    cfg.blockDim = dim3(256, 1, 1);
+    cfg.stream = stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, kparts_reduce_kernel, p.partials, p.out, p.rows, p.S, p.kparts);
     if (e != cudaSuccess) { *cuda_err = e; return I4MM_ERR_LAUNCH; }
+    count_launch();
     return I4MM_OK;
 }
 
@@ -1012,21 +1234,24 @@ int launch_nt(const UmmaParams& p_in, const __half* x, int n_groups, cudaStream_
     p.kparts = 1;
     using F = UFormat<BITS, SPARSE>;
     using C = Cfg<NT, PAIR>;
-    constexpr int kBStageBytes = 2 * (PAIR ? NT / 2 : NT) * 128;
+    constexpr int H = C::kHalves;
+    p.U = (p.N + 64 * H - 1) / (64 * H);
+    constexpr int kBStageBytes = H * (PAIR ? NT / 2 : NT) * 128;
     TensorMaps tm;
     const uint64_t R = SPARSE ? (uint64_t)p.N / 16 : (uint64_t)p.N * BITS / 32;
-    bool ok = encode_2d(&tm.x, x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, p.rows, p.N, PAIR ? NT / 2 : NT, 64, CU_TENSOR_MAP_SWIZZLE_128B);
-    ok = ok && encode_2d(&tm.w, p.matrix, CU_TENSOR_MAP_DATA_TYPE_INT32, 4, R, p.S, 2 * F::WROWS, 128, CU_TENSOR_MAP_SWIZZLE_NONE);
+    bool ok = C::kStream ? encode_x_blocks_cached(&tm.x, x, p.rows, p.N, NT, H)
+                         : encode_2d_cached(&tm.x, x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, p.rows, p.N, PAIR ? NT / 2 : NT, 64, CU_TENSOR_MAP_SWIZZLE_128B);
+    ok = ok && encode_2d_cached(&tm.w, p.matrix, CU_TENSOR_MAP_DATA_TYPE_INT32, 4, R, p.S, H * F::WROWS, 128, CU_TENSOR_MAP_SWIZZLE_NONE);
     if (SPARSE)
-        ok = ok && encode_2d(&tm.m, p.mask, CU_TENSOR_MAP_DATA_TYPE_INT32, 4, (uint64_t)p.N / 32, p.S, 2 * F::MROWS, 128,
+        ok = ok && encode_2d_cached(&tm.m, p.mask, CU_TENSOR_MAP_DATA_TYPE_INT32, 4, (uint64_t)p.N / 32, p.S, H * F::MROWS, 128,
                              CU_TENSOR_MAP_SWIZZLE_NONE);
     else
         tm.m = tm.w;
-    ok = ok && encode_2d(&tm.s, p.scales, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, n_groups, p.S, 2, 128, CU_TENSOR_MAP_SWIZZLE_NONE);
-    ok = ok && encode_2d(&tm.z, p.zeros, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, n_groups, p.S, 2, 128, CU_TENSOR_MAP_SWIZZLE_NONE);
+    ok = ok && encode_2d_cached(&tm.s, p.scales, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, n_groups, p.S, H, 128, CU_TENSOR_MAP_SWIZZLE_NONE);
+    ok = ok && encode_2d_cached(&tm.z, p.zeros, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, n_groups, p.S, H, 128, CU_TENSOR_MAP_SWIZZLE_NONE);
     if (!ok) return I4MM_ERR_DEVICE;
 
-    const size_t smem = 1024 + (size_t)ABStages<NT, PAIR>::value * kBStageBytes + (size_t)C::kWStages * WStage<F>::kBytes +
+    const size_t smem = 1024 + (size_t)ABStages<NT, PAIR>::value * kBStageBytes + (size_t)C::kWStages * WStage<F, H>::kBytes +
                         (!C::kEpiTransposed ? 0 : PAIR ? NT * 256 : 4096 * ((C::kEpiGroups == 2 && NT < 256) ? 2 : 1));
     auto kern = umma_kernel<BITS, SPARSE, NT, PAIR>;
     // per-device caches; atomics because two host threads may make their first call at once (both then compute the same values)
@@ -1056,16 +1281,18 @@ int launch_nt(const UmmaParams& p_in, const __half* x, int n_groups, cudaStream_
         // clusters of two CTAs; as many as can be resident at once, each walking its share of the pair tiles
         static std::atomic<int> max_clusters[16];
         cudaLaunchConfig_t cfg = {};
-        cudaLaunchAttribute attr[1];
+        cudaLaunchAttribute attr[2];
         attr[0].id = cudaLaunchAttributeClusterDimension;
         attr[0].val.clusterDim.x = 2;
         attr[0].val.clusterDim.y = 1;
         attr[0].val.clusterDim.z = 1;
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
         cfg.blockDim = dim3(C::kThreads, 1, 1);
         cfg.dynamicSmemBytes = smem;
         cfg.stream = stream;
         cfg.attrs = attr;
-        cfg.numAttrs = 1;
+        cfg.numAttrs = p.overlap ? 2 : 1;
         if (max_clusters[dev] == 0) {
             cfg.gridDim = dim3(2 * (sm_count[dev] / 2), 1, 1);
             int n = 0;
@@ -1087,7 +1314,7 @@ int launch_nt(const UmmaParams& p_in, const __half* x, int n_groups, cudaStream_
         e = cudaLaunchKernelEx(&cfg, kern, tm, p);
         if (e != cudaSuccess) { *cuda_err = e; return I4MM_ERR_LAUNCH; }
         count_launch();
-        g_last_shape = NT + 1000 + 10000 * p.kparts;
+        g_last_shape = NT + 1000 + 10000 * (p.kparts > 1 ? p.kparts : 0);
         if (p.kparts > 1) return launch_kparts_reduce(p, stream, cuda_err);
         return I4MM_OK;
     }
@@ -1098,11 +1325,26 @@ int launch_nt(const UmmaParams& p_in, const __half* x, int n_groups, cudaStream_
     const long long work = p.kparts > 1 ? n_tiles * p.kparts : C::kSplit ? n_tiles * p.U : n_tiles;
     if (grid > work || p.kparts > 1) grid = work;
     if (C::kSplit && grid > kPartialWords / C::kSlotElems) grid = kPartialWords / C::kSlotElems;   // one partial tile per CTA in the scratch
-    kern<<<(int)grid, C::kThreads, smem, stream>>>(tm, p);
-    e = cudaGetLastError();
+    {
+        // With `overlap` the kernel may start while the kernel before it in the stream is still running: its set-up and
+        // its copies of the weight-side tensors (which the caller has declared not to be written by that kernel) overlap
+        // that kernel's tail; everything that reads activations, reads or writes outputs or touches the scratch waits
+        // for that kernel inside (griddepcontrol.wait).
+        cudaLaunchConfig_t cfg = {};
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.gridDim = dim3((unsigned)grid, 1, 1);
+        cfg.blockDim = dim3(C::kThreads, 1, 1);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = stream;
+        cfg.attrs = attr;
+        cfg.numAttrs = p.overlap ? 1 : 0;
+        e = cudaLaunchKernelEx(&cfg, kern, tm, p);
+    }
     if (e != cudaSuccess) { *cuda_err = e; return I4MM_ERR_LAUNCH; }
     count_launch();
-    g_last_shape = NT + 10000 * p.kparts;
+    g_last_shape = NT + 10000 * (p.kparts > 1 ? p.kparts : 0);
     if (p.kparts > 1) return launch_kparts_reduce(p, stream, cuda_err);
     return I4MM_OK;
 }
@@ -1179,7 +1421,7 @@ bool umma_supported(int bits, bool sparse, int total_rows, int N, int S) {
 }
 
 int umma_launch(int bits, bool sparse, const StreamParams& sp, int total_rows, int n_groups, int group_size, int cta_pairs /* 0 by shape, 1 never */,
-                int force_nt /* 0 = by shape */, cudaStream_t stream, cudaError_t* cuda_err) {
+                int force_nt /* 0 = by shape */, int overlap, cudaStream_t stream, cudaError_t* cuda_err) {
     (void)group_size;
     UmmaParams p{};
     p.out = sp.out;
@@ -1192,9 +1434,10 @@ int umma_launch(int bits, bool sparse, const StreamParams& sp, int total_rows, i
     p.rows = total_rows;
     p.N = sp.N;
     p.S = sp.S;
-    p.U = (sp.N + 127) / 128;
+    p.U = 0;                      // set per configuration (units of 128 k or 256 k)
     p.CT = sp.CT;
     p.accumulate = sp.accumulate;
+    p.overlap = overlap;
     p.gdiv = sp.gdiv;
     if (sparse) return launch_fmt<4, true>(p, sp.x, n_groups, cta_pairs, force_nt, stream, cuda_err);
     if (bits == 4) return launch_fmt<4, false>(p, sp.x, n_groups, cta_pairs, force_nt, stream, cuda_err);

@@ -18,6 +18,17 @@ import torch
 from . import capi
 
 _workspaces: dict[tuple[int, int], torch.Tensor] = {}
+_static_weights = False
+
+
+def set_static_weights(flag: bool) -> None:
+    """Declare that the weight-side tensors (matrix, mask, scales, zeros) passed to the multiply entries are never
+    written by the kernel that precedes the call in the stream, as is the case for the weights of a loaded model.
+    Launches may then begin (set-up, first weight copies) while that kernel is still finishing; activations, outputs
+    and scratch are still only touched once it is complete.  Off by default: the reference orders every launch after
+    the whole preceding kernel, and a caller that rewrites weights right before a call relies on that."""
+    global _static_weights
+    _static_weights = bool(flag)
 
 
 class Int4MatmulError(RuntimeError):
@@ -115,7 +126,7 @@ def _mult(bits: int, route: str, outs, matrix, multiplier, scales, zeros, group_
         stream = torch.cuda.current_stream(dev)
         ws = workspace(dev, stream)
         status = lib.i4mm_quant_matmul(
-            bits, 1 if matvec else 0, path, outs.data_ptr(), matrix.data_ptr(),
+            bits, 1 if matvec else 0, path | (capi.PATH_STATIC_WEIGHTS if _static_weights else 0), outs.data_ptr(), matrix.data_ptr(),
             sparse_mask.data_ptr() if sparse else None, multiplier.data_ptr(), scales.data_ptr(), zeros.data_ptr(),
             batch * seq_len, in_size, out_size, scales.shape[0], group_size,
             ws.data_ptr(), ws.numel(), stream.cuda_stream)

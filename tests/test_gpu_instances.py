@@ -148,3 +148,43 @@ def test_status_word_is_reported_and_cleared_on_the_host():
     # the compiled module offers the same check
     import int4matmul_kernels_b200 as pkg
     pkg.load_extension().check_device_status()
+
+
+@pytest.mark.parametrize("m", [1, 16, 200])
+def test_overlapped_launches_keep_stream_order_for_activations_and_outputs(m):
+    """With the static-weights promise a launch may begin while the kernel before it is still running; what it reads
+    (activations, old outputs) and writes (outputs, scratch) must still see that kernel's results.  A chain in which
+    every call consumes the previous call's output, and a run of accumulating calls into one buffer, must give the
+    same bits as the ordinary launches."""
+    n = s = 1024
+    probs = [oracle.make_problem(4, n, s, m, 128, seed=500 + i, scale_lo=0.01, scale_hi=0.03) for i in range(4)]
+    devs = [device_problem(p) for p in probs]
+    x0 = to_dev(probs[0]["x"])
+
+    def chain():
+        h = x0
+        for d in devs * 3:
+            out = torch.zeros((1, m, s), dtype=torch.float16, device="cuda")
+            ops.quant_int4_linear_mult_mtx(out, d["matrix"], h, d["scales"], d["zeros"], 128, None)
+            h = ops.row_norm(0, out.view(m, s)).view(1, m, s)
+        acc = torch.zeros((1, m, s), dtype=torch.float16, device="cuda")
+        for d in devs * 3:                      # the matvec route (seq_len == 1) adds into acc; others overwrite
+            ops.quant_matmul(4, acc, d["matrix"], x0, d["scales"], d["zeros"], 128, None)
+        torch.cuda.synchronize()
+        return h.cpu().numpy(), acc.cpu().numpy()
+
+    plain = chain()
+    ops.set_static_weights(True)
+    try:
+        for _ in range(3):
+            over = chain()
+            assert np.array_equal(plain[0].view(np.uint16), over[0].view(np.uint16))
+            assert np.array_equal(plain[1].view(np.uint16), over[1].view(np.uint16))
+    finally:
+        ops.set_static_weights(False)
+    # and the first link of the chain against the oracle
+    out = torch.zeros((1, m, s), dtype=torch.float16, device="cuda")
+    ops.quant_int4_linear_mult_mtx(out, devs[0]["matrix"], x0, devs[0]["scales"], devs[0]["zeros"], 128, None)
+    want, _, bound = oracle.expected(probs[0])
+    assert_parity(out.cpu().numpy(), want, bound, f"first link m={m}")
+    ops.check_device_status()
