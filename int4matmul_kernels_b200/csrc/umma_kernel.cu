@@ -270,7 +270,10 @@ struct Cfg {
     // complete, expect_tx + the copy's issue another ~190): at 128 k per stage that alone is ~27 us for 16384 x 16384
     // weights on 148 SMs, so the weight-streaming shapes use 256-k units.
     static constexpr int kHalves = kStream ? 4 : 2;
-    static constexpr int kWStages = kStream ? 9 : NT <= 64 ? 8 : kDequantBound ? 6 : 3;
+    static constexpr int kWStages = kStream ? (NT <= 16 ? 9 : 6) : NT <= 64 ? 8 : kDequantBound ? 6 : 3;
+    // staging slots (units of look-ahead) for activation rows that are reordered on their way into the A / activation
+    // stages (umma_kernel's PERM)
+    static constexpr int kXStaging = 4;
     static constexpr int kWG = kStream ? 3 : kDequantBound ? 4 : 2;   // dequant warpgroups (4 warps each), taking units in turn
     static constexpr int kABStages = kStream ? 3 : NT == 128 ? 4 : 3;   // ring of (A in tensor memory, activation tile in shared memory) pairs, one unit per stage
     static constexpr bool kWGuard = kWStages % kWG != 0;
@@ -311,7 +314,6 @@ struct Barriers {
     unsigned long long w_full[kMaxWStages], w_empty[kMaxWStages];
     unsigned long long ab_full[kMaxABStages];  // 4 dequant warps + the activation producer (with its transaction bytes)
     unsigned long long ab_free[kMaxABStages];  // tcgen05.commit: the MMAs that read the stage are done
-    unsigned long long b_landed[kMaxABStages]; // permuted k order only: the activation tile's copy has arrived (the producer warp then reorders it)
     unsigned long long d_full, d_empty;
 };
 
@@ -338,11 +340,13 @@ struct TensorMaps {
 // PAIR: launched as clusters of two CTAs (two SMs) that run every MMA together (cta_group::2, M = 256): the pair's
 // tile is 256 weight columns x NT rows, each CTA dequantises its own 128 columns and loads only half of the rows of
 // the activation tile, which halves the L2 -> shared-memory traffic that bounds the many-row shapes.
-template <int BITS, bool SPARSE, int NT, bool PAIR>
+// PERM (up to 8 rows of dense int4 only): the cheaper k order of UFormat, with the activations reordered to match.
+template <int BITS, bool SPARSE, int NT, bool PAIR, bool PERM = false>
 __global__ void __launch_bounds__(Cfg<NT, PAIR>::kThreads, Cfg<NT, PAIR>::kMinBlocks)
-umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
+umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p, const __half* __restrict__ x) {
     using C = Cfg<NT, PAIR>;
-    using F = UFormat<BITS, SPARSE, C::kStream>;                     // weight-streaming shapes: the cheaper k order where the format has one
+    using F = UFormat<BITS, SPARSE, PERM>;
+    static_assert(!PERM || (C::kStream && F::kPermutedK), "the permuted k order is for dense int4 weight streaming");
     constexpr int H = C::kHalves;                                    // 64-k parts per unit
     using WS = WStage<F, H>;
     static_assert(!PAIR || (NT >= 128 && !C::kEpiHandoff), "CTA pairs are for the many-row shapes");
@@ -371,6 +375,7 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
     const uint32_t b_ring = smem0;
     const uint32_t w_ring = smem0 + kABStages * kBStageBytes;
     const uint32_t epi_tile = w_ring + C::kWStages * WS::kBytes;     // 4 KB transposition tile per epilogue warpgroup (NT >= 128)
+    const uint32_t x_staging = epi_tile;                             // weight-streaming shapes (no transposition tile): activation staging ring
 
     // ---- set-up, spread over warps so that nothing waits for one thread ----
     // The weight producer's warp initialises the weight ring's barriers itself and does not wait for the rest of the
@@ -394,7 +399,6 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
                 // a pair's stage is full when the dequant warps of both CTAs and both activation halves have arrived
                 ptx::mbar_init(ptx::smem_u32(&bars.ab_full[lane]), PAIR ? 4 + 4 + 1 : 4 + 1);
                 ptx::mbar_init(ptx::smem_u32(&bars.ab_free[lane]), 1);
-                ptx::mbar_init(ptx::smem_u32(&bars.b_landed[lane]), 1);
             }
             if (lane == 31) {
                 ptx::mbar_init(ptx::smem_u32(&bars.d_full), 1);
@@ -482,62 +486,61 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p) {
                 t += u1 - u0;
             }
         }
-    } else if (warp == kBProducer && C::kStream && F::kPermutedK) {
+    } else if (PERM && warp == kBProducer) {
         // =========================== activation tiles in the permuted k order: the whole warp ===========================
-        // Lane 0 keeps up to kABStages copies in flight (one 3-D copy per unit, natural k order); when a tile has landed,
-        // the warp reorders every 16-byte chunk (eight consecutive k) of its valid rows in place to
-        // (k0, k4, k1, k5, k2, k6, k3, k7), the order the dequant warps produce without byte shuffles, and only then
-        // announces the stage to the MMA warp.  A chunk stays where it is, so the 128-byte swizzle does not matter here.
+        // The few valid rows are fetched with plain asynchronous 16-byte copies (eight consecutive k each) into a small
+        // staging ring, kXStaging units ahead, every lane its own chunks.  When the unit's A / activation stage is free,
+        // each lane reorders its chunks to (k0, k4, k1, k5, k2, k6, k3, k7), the order the dequant warps produce without
+        // byte shuffles, and stores them at their place in the stage's 128-byte-swizzled tile; then the stage is
+        // announced to the MMA warp.  Rows past the last valid one are zeroed once, up front.  (A tensor-map copy plus
+        // a barrier per unit, as for the other formats, costs this warp more per unit than the unit may take.)
+        for (uint32_t o = lane * 16; o < (uint32_t)(kABStages * kBStageBytes); o += 32 * 16) ptx::sts128(b_ring + o, make_uint4(0, 0, 0, 0));
         ptx::grid_dependency_wait();      // the activations may be the output of the kernel before this one in the stream
+        constexpr int D = C::kXStaging;
         const int total = (int)(t_hi - t_lo);
-        int issued = 0;
-        bool ok = true;
-        for (int i = 0; i < total && ok; ++i) {
-            while (issued < total && issued < i + kABStages) {
-                const uint32_t s = (uint32_t)(issued % kABStages), ph = (uint32_t)(issued / kABStages) & 1u;
-                const uint32_t free_bar = ptx::smem_u32(&bars.ab_free[s]);
-                if (issued > i) {
-                    // look-ahead only while the stage is free: never wait for it with a landed tile still to reorder
-                    if (!ptx::mbar_test_wait(free_bar, ph ^ 1u)) break;
-                } else if (!ptx::mbar_wait(free_bar, ph ^ 1u)) {
-                    if (lane == 0) atomicExch(p.status, 12);
-                    ok = false;
-                    break;
-                }
-                if (lane == 0) {
-                    const long long t = t_lo + issued;
-                    const long long tile = div_nn(t, U);
-                    const int u = (int)(t - tile * U);
-                    const uint32_t landed = ptx::smem_u32(&bars.b_landed[s]);
-                    ptx::mbar_arrive_expect_tx(landed, (uint32_t)kBStageBytes);
-                    ptx::tma_load_3d(b_ring + s * kBStageBytes, &tm.x, 0, tile_mt(tile) * NT, u * H, landed);
-                }
-                ++issued;
+        const int nrows = min(NT, p.rows);                              // (one row tile: these shapes have at most NT rows)
+        const int n_chunks = nrows * 8 * H;                             // chunk index = row * (8 * H) + part * 8 + chunk of the part's 128-byte row segment
+        int u_next = (int)(t_lo - div_nn(t_lo, U) * U);                // unit (within its column tile) of the next copy
+        auto fetch = [&](int slot) {
+            for (int idx = lane; idx < n_chunks; idx += 32) {
+                const int r = idx / (8 * H), hc = idx % (8 * H);
+                const int k = (u_next * H * 8 + hc) * 8;
+                // past the end of the row (N is a multiple of 64, not of 256): zero fill
+                ptx::cp_async_16(x_staging + slot * kBStageBytes + idx * 16, x + (size_t)r * p.N + (k < p.N ? k : 0), k < p.N ? 16u : 0u);
             }
-            if (!ok) break;
+            ptx::cp_async_commit();
+            if (++u_next == (int)U) u_next = 0;
+        };
+        for (int j = 0; j < D - 1; ++j) {                                   // (always D - 1 groups, empty ones if need be: wait_group counts groups)
+            if (j < total) fetch(j);
+            else ptx::cp_async_commit();
+        }
+        for (int i = 0; i < total; ++i) {
+            if (i + D - 1 < total) fetch((i + D - 1) % D);
+            else ptx::cp_async_commit();                                  // (keeps the group count per iteration fixed)
             const uint32_t s = (uint32_t)(i % kABStages), ph = (uint32_t)(i / kABStages) & 1u;
-            if (!ptx::mbar_wait(ptx::smem_u32(&bars.b_landed[s]), ph)) {
-                if (lane == 0) atomicExch(p.status, 14);
+            if (!ptx::mbar_wait(ptx::smem_u32(&bars.ab_free[s]), ph ^ 1u)) {
+                if (lane == 0) atomicExch(p.status, 12);
                 break;
             }
-            const int mt = tile_mt(div_nn(t_lo + i, U));
-            const int nrows = min(NT, p.rows - mt * NT);
-            // chunk index = row * (8 * H) + part * 8 + chunk of the 128-byte row segment
-            for (int idx = lane; idx < nrows * 8 * H; idx += 32) {
+            ptx::cp_async_wait_group<D - 1>();                           // the copies of unit i (this lane's own chunks) have landed
+            const uint32_t src = x_staging + (i % D) * kBStageBytes, dst = b_ring + s * kBStageBytes;
+            for (int idx = lane; idx < n_chunks; idx += 32) {
                 const int r = idx / (8 * H), hc = idx % (8 * H);
-                const uint32_t addr = b_ring + s * kBStageBytes + (hc >> 3) * kBHalfBytes + r * 128 + (hc & 7) * 16;
-                const uint4 a = ptx::lds128(addr);
+                const uint4 a = ptx::lds128(src + idx * 16);
                 uint4 o;
                 o.x = prmt(a.x, a.z, 0x5410);      // (k0, k4)
                 o.y = prmt(a.x, a.z, 0x7632);      // (k1, k5)
                 o.z = prmt(a.y, a.w, 0x5410);      // (k2, k6)
                 o.w = prmt(a.y, a.w, 0x7632);      // (k3, k7)
-                ptx::sts128(addr, o);
+                // 128-byte swizzle of the tile a tensor-map copy would have produced: chunk c of row r sits at c ^ (r % 8)
+                ptx::sts128(dst + (hc >> 3) * kBHalfBytes + r * 128 + (((hc & 7) ^ (r & 7)) << 4), o);
             }
             ptx::fence_proxy_async_smem();         // the MMAs read the tile through the async proxy
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&bars.ab_full[s]));
         }
+        ptx::cp_async_wait_group<0>();
     } else if (warp == kBProducer) {
         // =========================== activation tiles, one 64-k sub-tile per part of a unit: one thread ===========================
         if (lane == 0) {
@@ -1228,7 +1231,7 @@ int launch_kparts_reduce(const UmmaParams& p, cudaStream_t stream, cudaError_t* 
     return I4MM_OK;
 }
 
-template <int BITS, bool SPARSE, int NT, bool PAIR>
+template <int BITS, bool SPARSE, int NT, bool PAIR, bool PERM = false>
 int launch_nt(const UmmaParams& p_in, const __half* x, int n_groups, cudaStream_t stream, cudaError_t* cuda_err) {
     UmmaParams p = p_in;
     p.kparts = 1;
@@ -1252,8 +1255,9 @@ int launch_nt(const UmmaParams& p_in, const __half* x, int n_groups, cudaStream_
     if (!ok) return I4MM_ERR_DEVICE;
 
     const size_t smem = 1024 + (size_t)ABStages<NT, PAIR>::value * kBStageBytes + (size_t)C::kWStages * WStage<F, H>::kBytes +
-                        (!C::kEpiTransposed ? 0 : PAIR ? NT * 256 : 4096 * ((C::kEpiGroups == 2 && NT < 256) ? 2 : 1));
-    auto kern = umma_kernel<BITS, SPARSE, NT, PAIR>;
+                        (!C::kEpiTransposed ? 0 : PAIR ? NT * 256 : 4096 * ((C::kEpiGroups == 2 && NT < 256) ? 2 : 1)) +
+                        (PERM ? (size_t)C::kXStaging * kBStageBytes : 0);
+    auto kern = umma_kernel<BITS, SPARSE, NT, PAIR, PERM>;
     // per-device caches; atomics because two host threads may make their first call at once (both then compute the same values)
     static std::atomic<int> ctas_per_sm[16];
     static std::atomic<int> sm_count[16];
@@ -1311,7 +1315,7 @@ int launch_nt(const UmmaParams& p_in, const __half* x, int n_groups, cudaStream_
         if (C::kSplit && clusters > kPartialWords / C::kSlotElems / 2) clusters = kPartialWords / C::kSlotElems / 2;
         if (clusters > work || p.kparts > 1) clusters = work;
         cfg.gridDim = dim3((unsigned)(2 * clusters), 1, 1);
-        e = cudaLaunchKernelEx(&cfg, kern, tm, p);
+        e = cudaLaunchKernelEx(&cfg, kern, tm, p, x);
         if (e != cudaSuccess) { *cuda_err = e; return I4MM_ERR_LAUNCH; }
         count_launch();
         g_last_shape = NT + 1000 + 10000 * (p.kparts > 1 ? p.kparts : 0);
@@ -1340,7 +1344,7 @@ int launch_nt(const UmmaParams& p_in, const __half* x, int n_groups, cudaStream_
         cfg.stream = stream;
         cfg.attrs = attr;
         cfg.numAttrs = p.overlap ? 1 : 0;
-        e = cudaLaunchKernelEx(&cfg, kern, tm, p);
+        e = cudaLaunchKernelEx(&cfg, kern, tm, p, x);
     }
     if (e != cudaSuccess) { *cuda_err = e; return I4MM_ERR_LAUNCH; }
     count_launch();
@@ -1399,7 +1403,11 @@ int launch_fmt(UmmaParams& p, const __half* x, int n_groups, int pair_mode, int 
         }
     }
     switch (nt) {
-        case 16: return launch_nt<BITS, SPARSE, 16, false>(p, x, n_groups, stream, cuda_err);
+        case 16:
+            // up to 8 rows of dense int4: the k order that needs no byte shuffles (more rows would cost the one warp
+            // that reorders the activations more per unit than the unit takes)
+            if (BITS == 4 && !SPARSE && p.rows <= 8) return launch_nt<BITS, SPARSE, 16, false, BITS == 4 && !SPARSE>(p, x, n_groups, stream, cuda_err);
+            return launch_nt<BITS, SPARSE, 16, false>(p, x, n_groups, stream, cuda_err);
         case 32: return launch_nt<BITS, SPARSE, 32, false>(p, x, n_groups, stream, cuda_err);
         case 64: return launch_nt<BITS, SPARSE, 64, false>(p, x, n_groups, stream, cuda_err);
         case 128: return launch_nt<BITS, SPARSE, 128, false>(p, x, n_groups, stream, cuda_err);
