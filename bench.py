@@ -322,6 +322,10 @@ def run_stack(args):
     from int4matmul_kernels_b200 import ops
     ops.set_static_weights(True)
     stack = sharding.DecoderStack(cfg, rank, world, dev)
+    if world > 1 and not args.nccl_gather:
+        # the multiply kernels store their columns into every rank's gathered buffers themselves (peer mappings); the
+        # pass then holds no collective library call and is captured as one CUDA graph per rank
+        stack.enable_peer_gather(m)
     gen = torch.Generator().manual_seed(4321)
     h_host = torch.randn((m, cfg.hidden), generator=gen).to(torch.float16).pin_memory()
     h0 = h_host.to(dev)
@@ -333,8 +337,8 @@ def run_stack(args):
         out = step()
     torch.cuda.synchronize()
     graph = None
-    # with collectives inside the step, the steps are launched directly (no graph capture of NCCL calls)
-    if not args.no_graph and world == 1:
+    # with NCCL all-gathers inside the step (--nccl-gather), the steps are launched directly (no graph capture of NCCL calls)
+    if not args.no_graph and (world == 1 or not args.nccl_gather):
         try:
             side = torch.cuda.Stream()
             side.wait_stream(torch.cuda.current_stream())
@@ -411,6 +415,43 @@ def run_stack(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms_e2e = float(t.item())
 
+    # ---- parity, outside the timed region: layer 0's q|k|v multiply of this rank's shard against the CPU oracle on
+    # sampled columns, and (several GPUs) the gathered buffer: this rank's block bit-equal to its own product, the
+    # whole buffer identical on every rank ----
+    x0 = stack.combine(0, h0)
+    w0 = stack.layers[0]["qkv"]
+    y_local = sharding.cuda_multiply(w0, x0)
+    torch.cuda.synchronize()
+    wl = dict(bits=4, n=w0.n, s=w0.s, m=m, g=cfg.group_size, sparse=False)
+    cols = sample_columns(w0.s, 48, rank)
+    n_el, n_bad, worst_ulp, exact = check_outputs(wl, [dict(matrix=w0.matrix, mask=None, scales=w0.scales, zeros=w0.zeros)],
+                                                  x0.cpu().numpy()[None], y_local, cols, False)
+    gather_ok = True
+    if world > 1:
+        parts = stack._linear(w0, x0, 3, "qkv")
+        torch.cuda.synchronize()
+        sp = w0.s // 3
+        for j in range(3):
+            gather_ok = gather_ok and bool(torch.equal(parts[j][:, rank * sp:(rank + 1) * sp], y_local[:, j * sp:(j + 1) * sp]))
+        digest = torch.cat([t.contiguous().view(torch.int16).to(torch.float64).sum().view(1) for t in parts])
+        lo, hi = digest.clone(), digest.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        gather_ok = gather_ok and bool(torch.equal(lo, hi))
+        t = torch.tensor([float(n_bad), 0.0 if gather_ok else 1.0, float(worst_ulp)], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        n_bad, gather_ok, worst_ulp = int(t[0].item()), t[1].item() == 0.0, int(t[2].item())
+    from int4matmul_kernels_b200 import ops as _ops
+    status_ok = True
+    try:
+        _ops.check_device_status()
+    except Exception:
+        status_ok = False
+    parity = dict(checked=True, ok=(n_bad == 0 and gather_ok and status_ok), out_of_tolerance=n_bad, max_ulp=worst_ulp,
+                  elements_per_rank=n_el, frac_bit_identical=exact, gathered_identical_on_all_ranks=gather_ok, ranks=world,
+                  device_status_ok=status_ok,
+                  against="CPU oracle on sampled columns of layer 0's q|k|v product of every rank's shard; gathered buffers compared across ranks")
+
     peaks = measured_peaks()
     peak = peaks["hbm"] if kind == "hbm" else peaks["tf_sustained"]
     achieved = value / world                                    # per GPU: every rank moves / computes 1/world of the pass
@@ -419,13 +460,14 @@ def run_stack(args):
             metric=metric, value=value, unit=unit, n_gpus=world, steps=args.steps, warmup=max(args.warmup, 3),
             ms_per_step=ms_step, higher_is_better=True, scaling="strong", vs_baseline=None, dtype="f16", data="synthetic",
             config=dict(workload=args.workload, layers=cfg.layers, hidden=cfg.hidden, mlp=cfg.mlp, m=m, bits=4, g=cfg.group_size,
-                        sharding=f"S columns of every matrix over {world} GPU(s), all-gather after each of the 4 launches per layer",
+                        sharding=(f"S columns of every matrix over {world} GPU(s); outputs gathered " +
+                                  ("by NCCL all-gathers" if args.nccl_gather else "by the multiply kernels' own peer stores + a flag hand-shake per matrix")),
                         l2=f"{cfg.layers * wpl // 2 / 1e9:.1f} GB of weights per pass (>> L2)",
                         timed_as="one CUDA graph of the K steps" if graph is not None else "K direct launches"),
             roofline=dict(bound=kind, achieved=achieved, peak=peak, unit=unit, frac=achieved / peak, traffic=None,
                           peak_source=peaks["source"], kernel="umma_kernel (tcgen05)",
                           note="whole pass incl. normalisation kernels and all-gathers, per GPU; sustained peak for tensor"),
-            cpu_baseline=None,
+            parity=parity, cpu_baseline=None,
             e2e=dict(value=units / (ms_e2e / args.steps / 1e3), unit=unit, h2d_bytes_per_step=h_host.numel() * 2,
                      d2h_bytes_per_step=out_host.numel() * 2, ms_per_step=ms_e2e / args.steps),
             clocks=clocks.summary(), gpu_launches=int(k_launches))))
@@ -757,6 +799,7 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-matvec", action="store_true", help="default workload only: do not time the matvec half of the metric as well")
     ap.add_argument("--no-graph", action="store_true", help="launch the timed steps directly instead of as one CUDA graph")
+    ap.add_argument("--nccl-gather", action="store_true", help="stack workloads on several GPUs: gather outputs with NCCL all-gathers (the checker path) instead of peer stores")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 0)
     if args.workload in STACK_WORKLOADS:

@@ -3,7 +3,7 @@
  *
  * This is the boundary a foreign-function binding attaches to.  Everything is plain pointers and
  * sizes; all data pointers are DEVICE pointers on the current CUDA device; nothing here allocates
- * device memory unless the entry says so; every launch goes onto the stream passed in (a
+ * device memory unless the entry says so (only i4mm_peer_buffer_create does); every launch goes onto the stream passed in (a
  * cudaStream_t cast to void*, NULL = the legacy default stream the reference launches on).
  * Calls return an i4mm_status; they never abort the process and never trap the device.
  *
@@ -97,6 +97,51 @@ int i4mm_quant_matmul(int bits, int accumulate, int path,
                       const void* x, const void* scales, const void* zeros,
                       int64_t rows, int64_t N, int64_t S, int64_t n_groups, int64_t group_size,
                       void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * The multiply of one rank of a column-sharded matrix, with the all-gather of the outputs done by the kernel's own
+ * stores.  No counterpart in the reference (which has no multi-GPU code); it serves the layer-stack configuration,
+ * where every matrix is sharded along S over the GPUs of one node and the next matrix needs all of S.
+ *
+ *   matrix, mask, scales, zeros   this rank's shard: S columns = `parts` pieces of S / parts columns each, piece j being
+ *                                 this rank's columns of the j-th matrix of a concatenation (q | k | v, gate | up; 1 = one matrix)
+ *   gathered[0 .. n_gathered)     (rows, ld) fp16 buffers, normally one per rank (this rank's own and the peers', opened
+ *                                 with i4mm_peer_buffer_open); the result is stored into every one of them, local column
+ *                                 c of piece j at column j * (S / parts) * world + rank * (S / parts) + c
+ *   ld >= S * world, a multiple of 8.  Always overwrites (no accumulate); tcgen05 kernel only (path 0, 2 or 3).
+ * The stores are plain global stores through the peer mappings; i4mm_gather_sync afterwards tells the peers and waits
+ * for them.  A buffer may be written again only after another i4mm_gather_sync has passed since its readers ran.
+ */
+int i4mm_quant_matmul_gather(int bits, int path, void* const* gathered, int n_gathered, int64_t ld, int64_t parts,
+                             int64_t rank, int64_t world, const void* matrix, const void* mask /* NULL = dense */,
+                             const void* x, const void* scales, const void* zeros,
+                             int64_t rows, int64_t N, int64_t S, int64_t n_groups, int64_t group_size,
+                             void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * Device buffers that other processes of the node can map (CUDA IPC), for i4mm_quant_matmul_gather.
+ *   create   cudaMalloc + zero-fill + export: *dev_ptr = the buffer, handle_out = i4mm_ipc_handle_bytes() bytes to send to the peers
+ *   open     map a peer's buffer from its handle (peer access is enabled on first use); close unmaps it
+ *   destroy  frees a buffer made by create (after the peers have closed it)
+ * These four and nothing else in the library allocate or free device memory.
+ */
+size_t i4mm_ipc_handle_bytes(void);
+int i4mm_peer_buffer_create(size_t bytes, void** dev_ptr, void* handle_out);
+int i4mm_peer_buffer_open(const void* handle, void** dev_ptr);
+int i4mm_peer_buffer_close(void* dev_ptr);
+int i4mm_peer_buffer_destroy(void* dev_ptr);
+
+/*
+ * Hand-shake after a gathering multiply.  Every rank has a flags buffer of i4mm_gather_flags_bytes(slots) bytes made
+ * with i4mm_peer_buffer_create (zero-filled) and opened by the peers; flags[r] = rank r's buffer as seen from here
+ * (flags[rank] = the local one).  The call enqueues one small kernel that, for slot `slot` (one slot per gathered
+ * buffer that is in flight at a time), tells every rank that this rank's stores are done and waits until every rank has
+ * said the same.  All ranks must issue the same sequence of calls.  The values exchanged advance by themselves on the
+ * device, so the call can be captured in a CUDA graph and replayed.  The wait is bounded (about two seconds): a peer
+ * that never arrives sets the status word of `workspace` (see i4mm_device_status) instead of hanging the GPU.
+ */
+size_t i4mm_gather_flags_bytes(int64_t slots);
+int i4mm_gather_sync(void* const* flags, int64_t world, int64_t rank, int64_t slot, int64_t slots, void* workspace, void* stream);
 
 /*
  * The same multiply as i4mm_quant_matmul on its streaming path, for callers that cannot allocate device

@@ -19,7 +19,7 @@ OBJ_DIR = os.path.join(LIB_DIR, "obj")
 INCLUDE_DIR = os.path.join(ROOT_DIR, "include")
 
 CAPI_LIB = os.path.join(LIB_DIR, "libint4matmul_b200.so")
-CUDA_SOURCES = ["capi.cu", "stream_kernel.cu", "umma_kernel.cu", "pack_kernel.cu", "noalloc.cu", "rownorm_kernel.cu"]
+CUDA_SOURCES = ["capi.cu", "stream_kernel.cu", "umma_kernel.cu", "pack_kernel.cu", "noalloc.cu", "rownorm_kernel.cu", "gather.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC"]
 

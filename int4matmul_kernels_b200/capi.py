@@ -30,6 +30,19 @@ _SIGNATURES = {
                                          ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
                                          ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
                                          ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]),
+    "i4mm_quant_matmul_gather": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, ctypes.POINTER(ctypes.c_void_p), ctypes.c_int,
+                                                ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
+                                                ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+                                                ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
+                                                ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]),
+    "i4mm_ipc_handle_bytes": (ctypes.c_size_t, []),
+    "i4mm_peer_buffer_create": (ctypes.c_int, [ctypes.c_size_t, ctypes.POINTER(ctypes.c_void_p), ctypes.c_void_p]),
+    "i4mm_peer_buffer_open": (ctypes.c_int, [ctypes.c_void_p, ctypes.POINTER(ctypes.c_void_p)]),
+    "i4mm_peer_buffer_close": (ctypes.c_int, [ctypes.c_void_p]),
+    "i4mm_peer_buffer_destroy": (ctypes.c_int, [ctypes.c_void_p]),
+    "i4mm_gather_flags_bytes": (ctypes.c_size_t, [ctypes.c_int64]),
+    "i4mm_gather_sync": (ctypes.c_int, [ctypes.POINTER(ctypes.c_void_p), ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
+                                        ctypes.c_int64, ctypes.c_void_p, ctypes.c_void_p]),
     "i4mm_quant_matvec_static": (ctypes.c_int, [ctypes.c_int, ctypes.c_int,
                                                 ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
                                                 ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,

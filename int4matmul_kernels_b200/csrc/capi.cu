@@ -70,11 +70,14 @@ unsigned long long i4mm_launch_count(void) { return i4mm::g_launches.load(); }
 
 size_t i4mm_workspace_bytes(void) { return kCounterBytes + kPartialBytes; }
 
-int i4mm_quant_matmul(int bits, int accumulate, int path,
-                      void* out, const void* matrix, const void* mask,
-                      const void* x, const void* scales, const void* zeros,
-                      int64_t rows, int64_t N, int64_t S, int64_t n_groups, int64_t group_size,
-                      void* workspace, size_t workspace_bytes, void* stream) {
+}  // extern "C"
+
+namespace {
+
+// The multiply behind both entries.  gather == nullptr: results go to `out` (rows, S).
+int multiply(int bits, int accumulate, int path, void* out, const i4mm::OutMap* gather, const void* matrix, const void* mask,
+             const void* x, const void* scales, const void* zeros, int64_t rows, int64_t N, int64_t S, int64_t n_groups,
+             int64_t group_size, void* workspace, size_t workspace_bytes, void* stream) {
     if (bits != 4 && bits != 3 && bits != 2) return I4MM_ERR_BITS;
     const bool sparse = mask != nullptr;
     if (sparse && bits != 4) return I4MM_ERR_UNSUPPORTED;
@@ -116,6 +119,16 @@ int i4mm_quant_matmul(int bits, int accumulate, int path,
     const uint32_t gq = group_size < 0 ? 0u : (uint32_t)(group_size / 64);
     p.gdiv.div = gq;
     p.gdiv.mul = gq >= 2 ? (uint32_t)((1ull << 32) / gq + 1ull) : 0u;    // gq == 0: one group -> index 0
+    if (gather) {
+        p.om = *gather;
+    } else {
+        p.om.dst[0] = (__half*)out;
+        p.om.n_dst = 1;
+        p.om.part_cols = (int)S;
+        p.om.ld = S;
+        p.om.part_stride = 0;
+        p.om.base = 0;
+    }
 
     if (!workspace || workspace_bytes < i4mm_workspace_bytes()) return I4MM_ERR_WORKSPACE;
     if (!aligned16(workspace)) return I4MM_ERR_ALIGN;
@@ -125,7 +138,7 @@ int i4mm_quant_matmul(int bits, int accumulate, int path,
 
     cudaStream_t st = (cudaStream_t)stream;
     bool use_umma = false;
-    if (path >= 2) {
+    if (path >= 2 || gather) {
         if (!i4mm::umma_supported(bits, sparse, (int)rows, (int)N, (int)S)) return I4MM_ERR_UNSUPPORTED;
         use_umma = true;
     } else if (path == 0) {
@@ -141,6 +154,43 @@ int i4mm_quant_matmul(int bits, int accumulate, int path,
     const cudaError_t e = i4mm::stream_launch(bits, sparse, p, (int)rows, kMaxStreamCtas, st);
     if (e != cudaSuccess) return fail_cuda(e);
     return I4MM_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int i4mm_quant_matmul(int bits, int accumulate, int path,
+                      void* out, const void* matrix, const void* mask,
+                      const void* x, const void* scales, const void* zeros,
+                      int64_t rows, int64_t N, int64_t S, int64_t n_groups, int64_t group_size,
+                      void* workspace, size_t workspace_bytes, void* stream) {
+    return multiply(bits, accumulate, path, out, nullptr, matrix, mask, x, scales, zeros, rows, N, S, n_groups, group_size,
+                    workspace, workspace_bytes, stream);
+}
+
+int i4mm_quant_matmul_gather(int bits, int path, void* const* gathered, int n_gathered, int64_t ld, int64_t parts,
+                             int64_t rank, int64_t world, const void* matrix, const void* mask, const void* x,
+                             const void* scales, const void* zeros, int64_t rows, int64_t N, int64_t S, int64_t n_groups,
+                             int64_t group_size, void* workspace, size_t workspace_bytes, void* stream) {
+    if (!gathered || n_gathered < 1 || n_gathered > i4mm::kMaxDst) return I4MM_ERR_SHAPE;
+    if (parts < 1 || world < 1 || rank < 0 || rank >= world || S <= 0 || S % parts != 0) return I4MM_ERR_SHAPE;
+    const int64_t part_cols = S / parts;                       // this shard's columns of one part
+    if (part_cols % 64 != 0 || ld < S * world || ld % 8 != 0) return I4MM_ERR_SHAPE;
+    i4mm::OutMap om{};
+    for (int d = 0; d < n_gathered; ++d) {
+        if (!gathered[d]) return I4MM_ERR_NULL;
+        if (!aligned16(gathered[d])) return I4MM_ERR_ALIGN;
+        om.dst[d] = (__half*)gathered[d];
+    }
+    om.n_dst = n_gathered;
+    om.part_cols = (int)part_cols;
+    om.ld = ld;
+    om.part_stride = part_cols * world;
+    om.base = rank * part_cols;
+    if ((path & 0xFF) == 1) return I4MM_ERR_UNSUPPORTED;      // the streaming kernel has no gathering epilogue
+    return multiply(bits, 0, path, gathered[0], &om, matrix, mask, x, scales, zeros, rows, N, S, n_groups, group_size,
+                    workspace, workspace_bytes, stream);
 }
 
 int i4mm_device_status(void* workspace, void* stream) {

@@ -73,6 +73,26 @@ struct GroupDiv {
     }
 };
 
+// ---- where results go ----------------------------------------------------------------------------------------------
+// The ordinary entry writes one (rows, S) array.  The gathering entry writes this rank's S columns into the same place
+// of up to 8 arrays (its own and its peers' gathered (rows, ld) buffers, reached through peer-mapped pointers with
+// plain stores): local column c belongs to part c / part_cols of a concatenation of matrices that were sharded one by
+// one (q | k | v, gate | up), and lands at column part * part_stride + base + c % part_cols.
+constexpr int kMaxDst = 8;
+struct OutMap {
+    __half* dst[kMaxDst];
+    int n_dst;
+    int part_cols;           // local columns per part (>= S: one part)
+    long long ld;            // row stride of every destination, in elements
+    long long part_stride;   // destination columns from one part to the next
+    long long base;          // destination column of local column 0
+    __device__ __forceinline__ long long col(int c) const {
+        if (c < part_cols) return base + c;
+        const int part = c / part_cols;
+        return part * part_stride + base + (c - part * part_cols);
+    }
+};
+
 // ---- parameters of the weight-streaming kernel ---------------------------------------------------
 struct StreamParams {
     __half* out;             // (rows, S)
@@ -90,6 +110,7 @@ struct StreamParams {
     int CT;                  // ceil(S / 128)
     int accumulate;          // out = half(float(out) + acc) instead of overwrite
     GroupDiv gdiv;
+    OutMap om;               // tcgen05 kernel only: destinations of the result (dst[0] == out for the ordinary entry)
 };
 
 // Counts kernel launches of this library in this process (read through i4mm_launch_count); defined in capi.cu.

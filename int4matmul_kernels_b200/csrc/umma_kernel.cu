@@ -45,7 +45,7 @@ enum : int { MODE_FAST = 0, MODE_GENERAL = 1, MODE_SLOW = 2 };
 
 
 struct UmmaParams {
-    __half* out;
+    OutMap om;           // where the results go (one array, or this rank's columns of several gathered arrays)
     const uint32_t* matrix;
     const uint32_t* mask;
     const __half* scales;
@@ -757,7 +757,7 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p, const __h
 #pragma unroll
                 for (int j = 0; j < 16; ++j)
                     if (j0 + j < nrows)
-                        v[j] = __float_as_uint(__uint_as_float(v[j]) + __half2float(p.out[(size_t)(row0 + j0 + j) * p.S + scol]));
+                        v[j] = __float_as_uint(__uint_as_float(v[j]) + __half2float(p.om.dst[0][(size_t)(row0 + j0 + j) * p.om.ld + p.om.col(scol)]));
             };
             if (C::kEpiTransposed) {
                 // 16 accumulator columns (= 16 output rows) at a time: transposed through a 4 KB shared-memory tile so that
@@ -806,7 +806,8 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p, const __h
                         const int m = eg * kShare + (idx >> 4), c8 = (idx & 15) * 8;
                         if (m < nrows && ct * 128 + c8 < p.S) {
                             const uint4 q = ptx::lds128(stage + (idx >> 4) * 256 + c8 * 2);
-                            *reinterpret_cast<uint4*>(p.out + (size_t)(row0 + m) * p.S + ct * 128 + c8) = q;
+                            const size_t at = (size_t)(row0 + m) * p.om.ld + p.om.col(ct * 128 + c8);   // (a chunk of 8 columns never straddles parts)
+                            for (int d = 0; d < p.om.n_dst; ++d) *reinterpret_cast<uint4*>(p.om.dst[d] + at) = q;
                         }
                     }
                     ptx::named_bar_sync(bar_id, 128);                       // the staging area may be written again
@@ -846,7 +847,8 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p, const __h
                         const int m = j0 + (idx >> 4), c8 = (idx & 15) * 8;
                         if (m < nrows && ct * 128 + c8 < p.S) {
                             const uint4 q = ptx::lds128(stage_tile + (idx >> 4) * 256 + c8 * 2);
-                            *reinterpret_cast<uint4*>(p.out + (size_t)(row0 + m) * p.S + ct * 128 + c8) = q;
+                            const size_t at = (size_t)(row0 + m) * p.om.ld + p.om.col(ct * 128 + c8);
+                            for (int d = 0; d < p.om.n_dst; ++d) *reinterpret_cast<uint4*>(p.om.dst[d] + at) = q;
                         }
                     }
                     ptx::named_bar_sync(bar_id, 128);
@@ -874,14 +876,16 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p, const __h
                     continue;
                 }
                 if (col_ok) {
+                    const long long dcol = p.om.col(scol);
 #pragma unroll
                     for (int j = 0; j < CH; ++j) {
                         const int m = j0 + j;
                         if (m < nrows) {
                             float f = __uint_as_float(v[j]);
-                            __half* o = p.out + (size_t)(row0 + m) * p.S + scol;
-                            if (p.accumulate) f += __half2float(*o);
-                            *o = __float2half_rn(f);
+                            const size_t at = (size_t)(row0 + m) * p.om.ld + dcol;
+                            if (p.accumulate) f += __half2float(p.om.dst[0][at]);
+                            const __half h = __float2half_rn(f);
+                            for (int d = 0; d < p.om.n_dst; ++d) p.om.dst[d][at] = h;
                         }
                     }
                 }
@@ -1061,12 +1065,13 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p, const __h
 
 // Sums the K parts written by umma_kernel (fp32, (part, row, S)) in part order, rounds once to fp16, and puts the
 // scratch back to all-zero (the split-K reduction of the few-row shapes relies on that).  8 columns per thread.
-__global__ void kparts_reduce_kernel(float* __restrict__ parts, __half* __restrict__ out, int rows, int S, int kparts) {
+__global__ void kparts_reduce_kernel(float* __restrict__ parts, const OutMap om, int rows, int S, int kparts) {
     // (launched with programmatic stream serialization: the next kernel may be scheduled at once, this one touches
     // nothing before the kernel that wrote the parts has completed)
     ptx::grid_launch_dependents();
     ptx::grid_dependency_wait();
-    const long long n8 = (long long)rows * S / 8;
+    const int s8 = S / 8;
+    const long long n8 = (long long)rows * s8;
     const size_t stride = (size_t)rows * S;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (long long)gridDim.x * blockDim.x) {
         float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
@@ -1081,7 +1086,10 @@ __global__ void kparts_reduce_kernel(float* __restrict__ parts, __half* __restri
         __half2 h[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) h[j] = __floats2half2_rn(acc[2 * j], acc[2 * j + 1]);
-        *reinterpret_cast<uint4*>(out + i * 8) = *reinterpret_cast<uint4*>(h);
+        const long long row = i / s8;
+        const int c8 = (int)(i - row * s8) * 8;
+        const size_t at = (size_t)row * om.ld + om.col(c8);
+        for (int d = 0; d < om.n_dst; ++d) *reinterpret_cast<uint4*>(om.dst[d] + at) = *reinterpret_cast<uint4*>(h);
     }
 }
 
@@ -1225,7 +1233,7 @@ int launch_kparts_reduce(const UmmaParams& p, cudaStream_t stream, cudaError_t* 
     cfg.stream = stream;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    const cudaError_t e = cudaLaunchKernelEx(&cfg, kparts_reduce_kernel, p.partials, p.out, p.rows, p.S, p.kparts);
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, kparts_reduce_kernel, p.partials, p.om, p.rows, p.S, p.kparts);
     if (e != cudaSuccess) { *cuda_err = e; return I4MM_ERR_LAUNCH; }
     count_launch();
     return I4MM_OK;
@@ -1432,7 +1440,7 @@ int umma_launch(int bits, bool sparse, const StreamParams& sp, int total_rows, i
                 int force_nt /* 0 = by shape */, int overlap, cudaStream_t stream, cudaError_t* cuda_err) {
     (void)group_size;
     UmmaParams p{};
-    p.out = sp.out;
+    p.om = sp.om;
     p.matrix = sp.matrix;
     p.mask = sp.mask;
     p.scales = sp.scales;

@@ -73,6 +73,103 @@ def cuda_multiply(w: QuantWeights, x: torch.Tensor) -> torch.Tensor:
     return out.view(x.shape[0], w.s)
 
 
+class _DevicePointerView:
+    """Lets torch wrap device memory that the library allocated (`torch.as_tensor` reads __cuda_array_interface__)."""
+
+    def __init__(self, ptr: int, shape: tuple, typestr: str):
+        self.__cuda_array_interface__ = dict(shape=shape, typestr=typestr, data=(ptr, False), version=3, strides=None)
+
+
+class PeerGather:
+    """Gathered output buffers that the multiply kernels of all ranks write into directly (`i4mm_quant_matmul_gather`).
+
+    Every rank allocates one (rows, S) fp16 buffer per name plus a flags buffer through the library
+    (`i4mm_peer_buffer_create`), the CUDA IPC handles go round the process group once, and every rank maps the others'
+    buffers.  After that a step runs no collective library call: the multiply's epilogue stores this rank's columns
+    into every rank's buffer through the peer mappings and `i4mm_gather_sync` is the hand-shake, so a pass can be
+    captured in one CUDA graph per rank.  With world == 1 the same calls run on local memory only."""
+
+    def __init__(self, shapes: dict, rank: int, world: int, device, group=None):
+        import ctypes
+        from . import capi
+        self.lib = capi.load()
+        self.rank, self.world, self.device = rank, world, torch.device(device)
+        self.names = list(shapes)
+        self.shapes = dict(shapes)
+        hb = self.lib.i4mm_ipc_handle_bytes()
+        self._owned, self._opened = [], []
+        local, handles = {}, {}
+        with torch.cuda.device(self.device):
+            for name, nbytes in [(n, r * ld * 2) for n, (r, ld) in shapes.items()] + [("__flags", self.lib.i4mm_gather_flags_bytes(len(shapes)))]:
+                ptr, h = ctypes.c_void_p(), ctypes.create_string_buffer(hb)
+                self._check(self.lib.i4mm_peer_buffer_create(nbytes, ctypes.byref(ptr), h), "peer buffer")
+                self._owned.append(ptr.value)
+                local[name], handles[name] = ptr.value, h.raw
+            everyone = [handles]
+            if world > 1:
+                everyone = [None] * world
+                dist.all_gather_object(everyone, handles, group=group)
+            self.ptrs = {}
+            for name in local:
+                row = []
+                for r in range(world):
+                    if r == rank:
+                        row.append(local[name])
+                    else:
+                        ptr = ctypes.c_void_p()
+                        self._check(self.lib.i4mm_peer_buffer_open(everyone[r][name], ctypes.byref(ptr)), "peer mapping")
+                        self._opened.append(ptr.value)
+                        row.append(ptr.value)
+                self.ptrs[name] = (ctypes.c_void_p * world)(*row)
+            self.buffers = {n: torch.as_tensor(_DevicePointerView(local[n], shapes[n], "<f2"), device=self.device) for n in shapes}
+        if world > 1:
+            dist.barrier(group=group)           # nobody writes before everybody has mapped
+
+    def _check(self, status: int, what: str) -> None:
+        from . import capi, ops
+        if status != capi.OK:
+            raise ops.Int4MatmulError(status, what)
+
+    def multiply(self, name: str, w: QuantWeights, x: torch.Tensor, parts: int = 1) -> list:
+        """x (rows, N) times this rank's shard `w`, written into every rank's gathered buffer `name`, then the hand-shake.
+        Returns the `parts` gathered matrices as column slices (rows, S_part) of the local buffer."""
+        from . import capi, ops
+        rows_max, ld = self.shapes[name]
+        rows = x.shape[0]
+        if rows > rows_max or w.s * self.world != ld:
+            raise ValueError("gathered buffer does not fit this multiply")
+        stream = torch.cuda.current_stream(self.device)
+        ws = ops.workspace(self.device, stream)
+        path = capi.PATH_AUTO | (capi.PATH_STATIC_WEIGHTS if ops._static_weights else 0)
+        self._check(self.lib.i4mm_quant_matmul_gather(
+            w.bits, path, self.ptrs[name], self.world, ld, parts, self.rank, self.world, w.matrix.data_ptr(),
+            w.mask.data_ptr() if w.mask is not None else None, x.data_ptr(), w.scales.data_ptr(), w.zeros.data_ptr(),
+            rows, w.n, w.s, w.scales.shape[0], w.group_size, ws.data_ptr(), ws.numel(), stream.cuda_stream), "gathering multiply")
+        self._check(self.lib.i4mm_gather_sync(self.ptrs["__flags"], self.world, self.rank, self.names.index(name), len(self.names),
+                                              ws.data_ptr(), stream.cuda_stream), "gather hand-shake")
+        buf = self.buffers[name][:rows]
+        sp = ld // parts
+        return [buf[:, i * sp:(i + 1) * sp] for i in range(parts)]
+
+    def close(self) -> None:
+        for ptr in self._opened:
+            self.lib.i4mm_peer_buffer_close(ptr)
+        self._opened = []
+
+    def destroy(self) -> None:
+        self.close()
+        for ptr in self._owned:
+            self.lib.i4mm_peer_buffer_destroy(ptr)
+        self._owned = []
+
+
+def gathered_column(c: int, part_cols: int, rank: int, world: int) -> int:
+    """Column of a gathered buffer that local column c of rank `rank`'s shard lands in (the kernels' OutMap): piece
+    c // part_cols of a concatenation whose matrices were sharded one by one."""
+    part = c // part_cols
+    return part * part_cols * world + rank * part_cols + c % part_cols
+
+
 class ShardedLinear:
     """A column shard of one quantized linear layer plus the gather of its outputs."""
 
@@ -180,8 +277,16 @@ class DecoderStack:
             self.layers.append(out)
         return self
 
-    def _linear(self, w: QuantWeights, x: torch.Tensor, parts: int) -> list[torch.Tensor]:
+    def enable_peer_gather(self, rows: int) -> None:
+        """From now on every matrix's outputs are gathered by the multiply kernels' own peer stores (PeerGather)
+        instead of an NCCL all-gather; `rows` = the largest number of activation rows that will be passed."""
+        shapes = {name: (rows, s) for name, _, s in self.cfg.matrices()}
+        self.peer = PeerGather(shapes, self.rank, self.world, self.layers[0]["qkv"].matrix.device, self.group)
+
+    def _linear(self, w: QuantWeights, x: torch.Tensor, parts: int, name: str = "") -> list[torch.Tensor]:
         """Local multiply + gather; returns the `parts` gathered tensors (rows, S_part)."""
+        if getattr(self, "peer", None) is not None:
+            return self.peer.multiply(name, w, x, parts)
         local = self.multiply(w, x)                                   # (rows, parts * S_part / P)
         rows = local.shape[0]
         if self.world == 1:
@@ -207,12 +312,12 @@ class DecoderStack:
     def forward(self, h: torch.Tensor) -> torch.Tensor:
         comb = self.combine
         for mats in self.layers:
-            q, k, v = self._linear(mats["qkv"], comb(0, h), 3)
+            q, k, v = self._linear(mats["qkv"], comb(0, h), 3, "qkv")
             t = comb(1, q, k, v)
-            (o,) = self._linear(mats["o"], t, 1)
+            (o,) = self._linear(mats["o"], t, 1, "o")
             h = comb(2, h, o)
-            gate, up = self._linear(mats["gate_up"], h, 2)
+            gate, up = self._linear(mats["gate_up"], h, 2, "gate_up")
             a = comb(3, gate, up)
-            (d,) = self._linear(mats["down"], a, 1)
+            (d,) = self._linear(mats["down"], a, 1, "down")
             h = comb(2, h, d)
         return h

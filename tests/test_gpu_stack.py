@@ -83,6 +83,33 @@ def _nccl_worker(rank, world, port, out_dir):
         a, b = full_stack.forward(h), mine.forward(h)
         torch.cuda.synchronize()
         assert torch.equal(a, b)
+        # the same stack with the outputs gathered by the multiply kernels' own peer stores: bit-equal, step after step,
+        # and replayed from one CUDA graph per rank (no collective library call inside the pass)
+        mine.enable_peer_gather(rows=5)
+        ops.set_static_weights(True)
+        for _ in range(3):
+            c = mine.forward(h)
+            torch.cuda.synchronize()
+            assert torch.equal(a, c), f"rank {rank}: peer gather differs"
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            mine.forward(h)
+        torch.cuda.synchronize()
+        dist.barrier()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            d = mine.forward(h)
+        for _ in range(3):
+            graph.replay()
+            torch.cuda.synchronize()
+            assert torch.equal(a, d), f"rank {rank}: graph replay of the peer-gather pass differs"
+        ops.set_static_weights(False)
+        ops.check_device_status()
+        dist.barrier()
+        mine.peer.close()
+        dist.barrier()
+        mine.peer.destroy()
         torch.save(b.cpu(), os.path.join(out_dir, f"rank{rank}.pt"))
     finally:
         dist.destroy_process_group()
@@ -96,3 +123,58 @@ def test_two_gpu_sharded_linear_and_stack_over_nccl(tmp_path):
         port = s.getsockname()[1]
     mp.spawn(_nccl_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
     assert torch.equal(torch.load(tmp_path / "rank0.pt"), torch.load(tmp_path / "rank1.pt"))
+
+
+@pytest.mark.parametrize("rows", [1, 16, 100, 300])
+@pytest.mark.parametrize("parts,world", [(1, 4), (3, 2), (2, 8)])
+def test_gathering_multiply_places_every_ranks_columns(rows, parts, world):
+    """One GPU standing in for `world` ranks ONE AFTER THE OTHER (no kernel waits for another here): each rank's shard,
+    multiplied by the gathering entry into the same (rows, S) buffer, must rebuild the unsharded product bit for bit,
+    with the matrices of a concatenation (q | k | v, gate | up) sharded one by one."""
+    import ctypes
+    from int4matmul_kernels_b200 import capi
+    lib = capi.load()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    n, s_part = 512, 64 * 3 * world                   # 192 columns per rank and part: tiles straddle part boundaries
+    s = parts * s_part
+    p = oracle.make_problem(4, n, s, rows, 128, seed=rows + parts)
+    full = sharding.QuantWeights(4, n, s, 128, torch.from_numpy(p["matrix"]).to(dev), torch.from_numpy(p["scales"]).to(dev),
+                                 torch.from_numpy(p["zeros"]).to(dev))
+    x = torch.from_numpy(p["x"][0]).to(dev)
+    want = sharding.cuda_multiply(full, x)
+    gathered = torch.full((rows, s), 7.0, dtype=torch.float16, device=dev)
+    ws = ops.workspace(dev, torch.cuda.current_stream())
+    for rank in range(world):
+        def cut(t):
+            return torch.cat([packing.shard_columns(t[..., j * s_part:(j + 1) * s_part], rank, world) for j in range(parts)], dim=-1).contiguous()
+        m, sc, z = cut(full.matrix), cut(full.scales), cut(full.zeros)
+        ptrs = (ctypes.c_void_p * 1)(gathered.data_ptr())
+        st = lib.i4mm_quant_matmul_gather(4, capi.PATH_AUTO, ptrs, 1, s, parts, rank, world, m.data_ptr(), None, x.data_ptr(),
+                                          sc.data_ptr(), z.data_ptr(), rows, n, s // world, sc.shape[0], 128,
+                                          ws.data_ptr(), ws.numel(), torch.cuda.current_stream().cuda_stream)
+        assert st == capi.OK
+    torch.cuda.synchronize()
+    assert torch.equal(gathered, want)
+    # the hand-shake of a single rank passes at once, and again (its values advance on the device)
+    peer = sharding.PeerGather({"g": (rows, s)}, 0, 1, dev)
+    for _ in range(2):
+        (y,) = peer.multiply("g", full, x, 1)
+        torch.cuda.synchronize()
+        assert torch.equal(y, want)
+    ops.check_device_status()
+    peer.destroy()
+
+
+def test_gathering_entry_rejects_bad_arguments():
+    import ctypes
+    from int4matmul_kernels_b200 import capi
+    lib = capi.load()
+    ptrs = (ctypes.c_void_p * 1)(16)
+    call = lambda **k: lib.i4mm_quant_matmul_gather(4, k.get("path", 0), ptrs, k.get("n", 1), k.get("ld", 512), k.get("parts", 1),
+                                                    k.get("rank", 0), k.get("world", 2), 16, None, 16, 16, 16, 1, 128, k.get("s", 256), 1, 128, 16, 1 << 30, None)
+    assert call(n=9) == capi.ERR_SHAPE
+    assert call(rank=2) == capi.ERR_SHAPE
+    assert call(ld=256) == capi.ERR_SHAPE                       # narrower than S * world
+    assert call(parts=3) == capi.ERR_SHAPE                      # S not divisible
+    assert call(parts=8, s=256) == capi.ERR_SHAPE               # 32 columns per piece: not a multiple of 64
+    assert call(path=1) == capi.ERR_UNSUPPORTED                 # the streaming kernel has no gathering epilogue

@@ -86,3 +86,21 @@ def test_stack_config_matches_the_benchmark_shapes():
     assert cfg.weights_per_layer() == 317_194_240                      # 4 x 5120^2 + 3 x 5120 x 13824
     names = [m[0] for m in cfg.matrices()]
     assert names == ["qkv", "o", "gate_up", "down"]
+
+
+def test_gathered_column_map_is_a_part_major_permutation():
+    """The column map of the gathering multiply (OutMap in the kernels, `gathered_column` here): over all ranks the
+    shards' columns fill the gathered buffer exactly once, piece by piece, ranks in order inside a piece."""
+    from int4matmul_kernels_b200 import sharding
+    for parts, world, part_cols in [(1, 8, 640), (3, 8, 640), (2, 8, 1728), (2, 2, 64)]:
+        s_local = parts * part_cols
+        seen = {}
+        for rank in range(world):
+            for c in range(s_local):
+                g = sharding.gathered_column(c, part_cols, rank, world)
+                assert g not in seen
+                seen[g] = (rank, c)
+        assert sorted(seen) == list(range(s_local * world))
+        for g, (rank, c) in seen.items():
+            piece, inside = divmod(g, part_cols * world)
+            assert piece == c // part_cols and inside // part_cols == rank and inside % part_cols == c % part_cols
