@@ -15,6 +15,7 @@
 #include <cstring>
 
 #include "common.cuh"
+#include "ptx.cuh"
 
 namespace {
 
@@ -29,6 +30,10 @@ struct PeerFlags {
 // kernel can be replayed from a CUDA graph: every rank runs the same sequence of calls, hence the same epochs.
 __global__ void gather_sync_kernel(PeerFlags pf, unsigned int* epochs, int* status, int world, int rank, int slot, int slots) {
     __shared__ unsigned int s_epoch;
+    // launched with programmatic stream serialization: the kernel after this one may be scheduled at once (it waits for
+    // this one itself before it reads anything), and nothing happens here before the multiply has completed
+    i4mm::ptx::grid_launch_dependents();
+    i4mm::ptx::grid_dependency_wait();
     if (threadIdx.x == 0) s_epoch = ++epochs[slot];
     __syncthreads();
     const unsigned int epoch = s_epoch;
@@ -119,8 +124,16 @@ int i4mm_gather_sync(void* const* flags, int64_t world, int64_t rank, int64_t sl
     }
     unsigned int* epochs = pf.flags[rank] + (size_t)slots * i4mm::kMaxDst;
     int* status = (int*)((char*)workspace + 256 * 1024 - 64);      // the workspace's status word (see i4mm_device_status)
-    gather_sync_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(pf, epochs, status, (int)world, (int)rank, (int)slot, (int)slots);
-    const cudaError_t e = cudaGetLastError();
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.gridDim = dim3(1, 1, 1);
+    cfg.blockDim = dim3(32, 1, 1);
+    cfg.stream = (cudaStream_t)stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, gather_sync_kernel, pf, epochs, status, (int)world, (int)rank, (int)slot, (int)slots);
     if (e != cudaSuccess) return fail(e);
     i4mm::count_launch();
     return I4MM_OK;
