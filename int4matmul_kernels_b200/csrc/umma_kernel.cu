@@ -675,22 +675,6 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p, const __h
             const int mt = tile_mt(tile), ct = tile_ct(tile);
             const int col = (warp & 3) * 32 + lane;
             const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
-            if (C::kEpiHandoff) {
-                ptx::named_bar_sync(2, 128 + 32);          // released by the MMA warp once the accumulator is complete
-                if (s_abort) return false;
-            } else {
-                bool got = ptx::mbar_wait(ptx::smem_u32(&bars.d_full), seg & 1u);
-                if (!got && lane == 0) atomicExch(p.status, 33);
-                if (C::kEpiTransposed) {
-                    // the four warps of an epilogue group meet at named barriers further down: a give-up has to be
-                    // the whole group's decision, or the warps that went on would wait there for ever
-                    if (!got) s_abort = 1;
-                    ptx::named_bar_sync(1 + 3 * ((warp - kEpiWarp0) >> 2), 128);
-                    got = s_abort == 0;
-                }
-                if (!got) return false;
-            }
-            ptx::tc_fence_after_sync();
             const bool complete = (u0 == 0) && (u1 == (int)U);
             const int scol = ct * 128 + col;
             const bool col_ok = scol < p.S;
@@ -759,6 +743,37 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p, const __h
                     }
                 }
             };
+            // The weight-streaming shapes fetch the other CTAs' partial tiles BEFORE the own accumulator is complete (the
+            // partners delivered them early in their run, as their first segment, and these warps have nothing else to
+            // do): their sum, in CTA order, then only has to be added, and the dependent round trips to L2 are off the tail.
+            constexpr int kPre = (C::kSplit && C::kEpiHandoff) ? C::kDCols : 1;
+            uint32_t pre[kPre];
+            bool prefetched = false;
+            if (C::kSplit && C::kEpiHandoff && !slot && b_hi > b_lo) {
+#pragma unroll
+                for (int j = 0; j < kPre; ++j) pre[j] = 0u;
+                if (kPre >= 16) {
+#pragma unroll
+                    for (int j0 = 0; j0 < kPre; j0 += 16) add_partials(reinterpret_cast<uint32_t(&)[16]>(pre[j0 < kPre ? j0 : 0]), j0);
+                }
+                prefetched = true;
+            }
+            if (C::kEpiHandoff) {
+                ptx::named_bar_sync(2, 128 + 32);          // released by the MMA warp once the accumulator is complete
+                if (s_abort) return false;
+            } else {
+                bool got = ptx::mbar_wait(ptx::smem_u32(&bars.d_full), seg & 1u);
+                if (!got && lane == 0) atomicExch(p.status, 33);
+                if (C::kEpiTransposed) {
+                    // the four warps of an epilogue group meet at named barriers further down: a give-up has to be
+                    // the whole group's decision, or the warps that went on would wait there for ever
+                    if (!got) s_abort = 1;
+                    ptx::named_bar_sync(1 + 3 * ((warp - kEpiWarp0) >> 2), 128);
+                    got = s_abort == 0;
+                }
+                if (!got) return false;
+            }
+            ptx::tc_fence_after_sync();
             // matvec route with more than 64 rows (a batch of one-row products): the caller's old values of rows
             // j0 .. of this lane's column are added to the unrounded sums, so that there is still one rounding
             auto add_old_outs = [&](uint32_t (&v)[16], int j0) {
@@ -879,7 +894,15 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p, const __h
                     put_partial(v, j0);
                     continue;
                 }
-                if (C::kSplit && b_hi > b_lo) add_partials(v, j0);
+                if (C::kSplit && b_hi > b_lo) {
+                    if (prefetched) {
+#pragma unroll
+                        for (int j = 0; j < CH; ++j)
+                            v[j] = __float_as_uint(__uint_as_float(v[j]) + __uint_as_float(pre[(j0 + j) < kPre ? j0 + j : 0]));
+                    } else {
+                        add_partials(v, j0);
+                    }
+                }
                 if (p.kparts > 1) {
                     put_kpart(v, j0);
                     continue;
