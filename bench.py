@@ -687,6 +687,14 @@ def run_workload(args, name, w, ctx):
     if not args.no_e2e:
         s_in, s_k, s_out = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
         x_dev = [torch.empty_like(x) for _ in range(2)]
+        # several GPUs: every rank needs all of x, but only 1 / N of it crosses this rank's PCIe link; the ranks then
+        # exchange their pieces over NVLink (one NCCL all-gather per step, inside the timed region)
+        # (only worth a collective's latency when x is large: a matvec's 32 KB go straight to every GPU)
+        split_x = world > 1 and x_host.numel() % (8 * world) == 0 and x_host.numel() * 2 >= (1 << 20)
+        if split_x:
+            chunk = x_host.numel() // world
+            x_piece_host = x_host.view(-1)[rank * chunk:(rank + 1) * chunk]
+            x_piece_dev = [torch.empty(chunk, dtype=torch.float16, device=dev) for _ in range(2)]
         o_dev = [torch.zeros((1, w["m"], s_local), dtype=torch.float16, device=dev) for _ in range(2)]
         out_host = [torch.empty((1, w["m"], s_local), dtype=torch.float16).pin_memory() for _ in range(2)]
         ev_in = [torch.cuda.Event() for _ in range(2)]
@@ -698,7 +706,11 @@ def run_workload(args, name, w, ctx):
             L = layers[i % copies]
             with torch.cuda.stream(s_in):
                 s_in.wait_event(ev_k[b])                   # the kernel that last read this input buffer
-                x_dev[b].copy_(x_host, non_blocking=True)
+                if split_x:
+                    x_piece_dev[b].copy_(x_piece_host, non_blocking=True)
+                    dist.all_gather_into_tensor(x_dev[b].view(-1), x_piece_dev[b])
+                else:
+                    x_dev[b].copy_(x_host, non_blocking=True)
                 ev_in[b].record(s_in)
             with torch.cuda.stream(s_k):
                 s_k.wait_event(ev_in[b])
@@ -739,10 +751,12 @@ def run_workload(args, name, w, ctx):
         n, b, u, fe = check_outputs(w, [layers[last % copies]], x_cpu, out_host[last % 2].to(dev), cols, matvec)
         checked, bad, worst_ulp, exact, n_cols = checked + n, bad + b, max(worst_ulp, u), min(exact, fe), n_cols + len(cols)
         e2e = dict(value=units_per_step(w, kind) / (ms_e2e / args.steps / 1e3), unit=unit,
-                   h2d_bytes_per_step=x_host.numel() * 2, d2h_bytes_per_step=out_host[0].numel() * 2,
+                   h2d_bytes_per_step=(x_host.numel() // world if split_x else x_host.numel()) * 2,
+                   d2h_bytes_per_step=out_host[0].numel() * 2, bytes_are="per rank (every rank copies its piece of x in and its columns of the result out)",
                    ms_per_step=ms_e2e / args.steps,
                    how="int4matmul.quant_matmul on pinned host buffers; input copy, kernel and result copy of consecutive steps "
-                       "overlap on three streams (double-buffered)")
+                       "overlap on three streams (double-buffered)" +
+                       ("; every rank copies 1 / N of x from the host and the ranks all-gather it over NVLink (NCCL)" if split_x else ""))
 
     if world > 1:
         t = torch.tensor([float(checked), float(bad), float(n_cols)], device=dev)
