@@ -196,8 +196,10 @@ int i4mm_check_mask(const void* mask, int64_t N, int64_t S, void* violations, vo
 /*
  * Row-wise glue of the layer-stack runner: y[r, :] = v / rms(v) per row, computed in fp32, with
  *   mode 0: v = a     mode 1: v = a + b + c     mode 2: v = a + b / rms(b)     mode 3: v = a * b
+ *   mode 4: mode 2 into y[0 : rows*width], then mode 0 of that (rounded) result into y[rows*width : 2*rows*width]
+ *           (a layer's residual stream and the next layer's normalised input from one launch)
  * a, b, c fp16 (rows, width) with row strides in elements (column slices of a gathered buffer are fine);
- * y fp16 (rows, width) contiguous; width even; pointers 4-byte aligned.  No counterpart in the reference
+ * y fp16 (rows, width) contiguous ((2, rows, width) in mode 4); width even; pointers 4-byte aligned.  No counterpart in the reference
  * (it has no model code): it replaces the handful of eager elementwise kernels between two quantized linears.
  */
 int i4mm_row_norm(int mode, void* y, const void* a, const void* b, const void* c, int64_t rows, int64_t width,

@@ -208,7 +208,7 @@ int i4mm_device_status(void* workspace, void* stream) {
 
 int i4mm_row_norm(int mode, void* y, const void* a, const void* b, const void* c, int64_t rows, int64_t width,
                   int64_t stride_a, int64_t stride_b, int64_t stride_c, void* stream) {
-    if (mode < 0 || mode > 3 || rows < 0 || width <= 0 || width % 2 != 0 || width > (1 << 30) || rows > (1ll << 31) - 1)
+    if (mode < 0 || mode > 4 || rows < 0 || width <= 0 || width % 2 != 0 || width > (1 << 30) || rows > (1ll << 31) - 1)
         return I4MM_ERR_SHAPE;
     if (rows == 0) return I4MM_OK;
     if (!y || !a || (mode != 0 && !b) || (mode == 1 && !c)) return I4MM_ERR_NULL;

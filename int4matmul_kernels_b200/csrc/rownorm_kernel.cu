@@ -1,6 +1,11 @@
 // Row-wise glue between the quantized linears of the layer-stack runner: one launch instead of the five to eight
 // elementwise / reduction kernels the same expression costs in eager PyTorch.  y = v / rms(v) per row, in fp32, with
 //   mode 0: v = a            mode 1: v = a + b + c            mode 2: v = a + b / rms(b)            mode 3: v = a * b
+//   mode 4: mode 2, followed in the same launch by mode 0 of its (rounded) result: two outputs, y and y + rows * width
+//           (the residual stream of a layer and the normalised input of the next layer's first linear)
+// Rows of up to kCachedWidth elements are read once and kept in registers over the reductions (one block of 512 threads
+// per row: the few-row passes are a chain of dependent launches, so a launch's latency is what counts); wider rows take
+// the kernel that re-reads its inputs per pass.
 // Inputs are fp16 rows of `width` elements with their own row strides (gathered q | k | v and gate | up are column
 // slices of one buffer); the output is contiguous.  No counterpart in the reference, which has no model code.
 #include "common.cuh"
@@ -69,6 +74,74 @@ __global__ void __launch_bounds__(256) rownorm_kernel(__half* __restrict__ y, co
     }
 }
 
+constexpr int kCachedThreads = 512;
+constexpr int kCachedPer = 14;                                     // fp16 pairs per thread
+constexpr int kCachedWidth = 2 * kCachedThreads * kCachedPer;      // 14336
+
+template <int MODE>
+__global__ void __launch_bounds__(kCachedThreads) rownorm_cached_kernel(__half* __restrict__ y, const __half* __restrict__ a,
+                                                                        const __half* __restrict__ b, const __half* __restrict__ c,
+                                                                        int width, long long sa, long long sb, long long sc,
+                                                                        long long second_output) {
+    __shared__ float red[32];
+    ptx::grid_launch_dependents();        // as in rownorm_kernel
+    ptx::grid_dependency_wait();
+    constexpr bool kHasB = MODE != 0, kHasC = MODE == 1, kInnerNorm = MODE == 2 || MODE == 4;
+    const long long row = blockIdx.x;
+    const __half2* a2 = reinterpret_cast<const __half2*>(a + row * sa);
+    const __half2* b2 = kHasB ? reinterpret_cast<const __half2*>(b + row * sb) : nullptr;
+    const __half2* c2 = kHasC ? reinterpret_cast<const __half2*>(c + row * sc) : nullptr;
+    __half2* y2 = reinterpret_cast<__half2*>(y + row * (long long)width);
+    const int n2 = width >> 1;
+    auto pair_at = [&](const __half2* src, int i) -> float2 {     // zero beyond the row: adds nothing to the sums
+        return __half22float2(u32_as_h2(i < n2 ? reinterpret_cast<const uint32_t*>(src)[i] : 0u));
+    };
+    float2 v[kCachedPer], vb[kCachedPer];
+#pragma unroll
+    for (int k = 0; k < kCachedPer; ++k) {                       // every load of the row is in flight at once
+        const int i = threadIdx.x + k * kCachedThreads;
+        v[k] = pair_at(a2, i);
+        if constexpr (kHasB) vb[k] = pair_at(b2, i);
+        if constexpr (kHasC) {
+            const float2 vc = pair_at(c2, i);
+            v[k] = make_float2(v[k].x + vb[k].x + vc.x, v[k].y + vb[k].y + vc.y);
+        }
+        if constexpr (MODE == 3) v[k] = make_float2(v[k].x * vb[k].x, v[k].y * vb[k].y);
+    }
+    if constexpr (kInnerNorm) {
+        float s = 0.f;
+#pragma unroll
+        for (int k = 0; k < kCachedPer; ++k) s += vb[k].x * vb[k].x + vb[k].y * vb[k].y;
+        const float rb = rsqrtf(block_sum(s, red) / (float)width + 1e-6f);
+#pragma unroll
+        for (int k = 0; k < kCachedPer; ++k) v[k] = make_float2(v[k].x + vb[k].x * rb, v[k].y + vb[k].y * rb);
+    }
+    float s = 0.f;
+#pragma unroll
+    for (int k = 0; k < kCachedPer; ++k) s += v[k].x * v[k].x + v[k].y * v[k].y;
+    const float r = rsqrtf(block_sum(s, red) / (float)width + 1e-6f);
+    float s2 = 0.f;
+#pragma unroll
+    for (int k = 0; k < kCachedPer; ++k) {
+        const int i = threadIdx.x + k * kCachedThreads;
+        const __half2 h = __floats2half2_rn(v[k].x * r, v[k].y * r);
+        if (i < n2) y2[i] = h;
+        if constexpr (MODE == 4) {
+            v[k] = __half22float2(h);                            // the second norm sees the rounded values, as a second launch would
+            s2 += v[k].x * v[k].x + v[k].y * v[k].y;
+        }
+    }
+    if constexpr (MODE == 4) {
+        const float r2 = rsqrtf(block_sum(s2, red) / (float)width + 1e-6f);
+        __half2* z2 = y2 + (second_output >> 1);
+#pragma unroll
+        for (int k = 0; k < kCachedPer; ++k) {
+            const int i = threadIdx.x + k * kCachedThreads;
+            if (i < n2) z2[i] = __floats2half2_rn(v[k].x * r2, v[k].y * r2);
+        }
+    }
+}
+
 }  // namespace
 
 cudaError_t rownorm_launch(int mode, void* y, const void* a, const void* b, const void* c, long long rows, int width,
@@ -86,6 +159,27 @@ cudaError_t rownorm_launch(int mode, void* y, const void* a, const void* b, cons
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     cudaError_t e;
+    const long long second = rows * (long long)width;             // mode 4: element offset of the second output
+    if (width <= kCachedWidth) {
+        cfg.blockDim = dim3(kCachedThreads, 1, 1);
+        switch (mode) {
+            case 0: e = cudaLaunchKernelEx(&cfg, rownorm_cached_kernel<0>, yy, aa, bb, cc, width, sa, sb, sc, second); break;
+            case 1: e = cudaLaunchKernelEx(&cfg, rownorm_cached_kernel<1>, yy, aa, bb, cc, width, sa, sb, sc, second); break;
+            case 2: e = cudaLaunchKernelEx(&cfg, rownorm_cached_kernel<2>, yy, aa, bb, cc, width, sa, sb, sc, second); break;
+            case 3: e = cudaLaunchKernelEx(&cfg, rownorm_cached_kernel<3>, yy, aa, bb, cc, width, sa, sb, sc, second); break;
+            default: e = cudaLaunchKernelEx(&cfg, rownorm_cached_kernel<4>, yy, aa, bb, cc, width, sa, sb, sc, second); break;
+        }
+        if (e == cudaSuccess) count_launch();
+        return e;
+    }
+    if (mode == 4) {                                              // wide rows: the two steps as two launches
+        e = cudaLaunchKernelEx(&cfg, rownorm_kernel<2>, yy, aa, bb, cc, width, sa, sb, sc);
+        if (e != cudaSuccess) return e;
+        count_launch();
+        e = cudaLaunchKernelEx(&cfg, rownorm_kernel<0>, yy + second, (const __half*)yy, bb, cc, width, (long long)width, sb, sc);
+        if (e == cudaSuccess) count_launch();
+        return e;
+    }
     switch (mode) {
         case 0: e = cudaLaunchKernelEx(&cfg, rownorm_kernel<0>, yy, aa, bb, cc, width, sa, sb, sc); break;
         case 1: e = cudaLaunchKernelEx(&cfg, rownorm_kernel<1>, yy, aa, bb, cc, width, sa, sb, sc); break;

@@ -196,12 +196,13 @@ def weight_matrix_packing(wt_outs, msk_outs, wt_in, msk_in) -> None:
 
 def row_norm(mode: int, a: torch.Tensor, b: torch.Tensor | None = None, c: torch.Tensor | None = None) -> torch.Tensor:
     """Row-wise glue of the layer-stack runner (`i4mm_row_norm`): v / rms(v) per row with
-    v = a (mode 0), a + b + c (1), a + b / rms(b) (2), a * b (3).  Inputs fp16 (rows, width), last dim contiguous."""
+    v = a (mode 0), a + b + c (1), a + b / rms(b) (2), a * b (3).  Inputs fp16 (rows, width), last dim contiguous.
+    Mode 4 returns (2, rows, width): mode 2's result, and mode 0 of that result, from one launch."""
     rows, width = a.shape
     for t in (a, b, c):
         if t is not None and (t.dtype != torch.float16 or t.stride(-1) != 1 or tuple(t.shape) != (rows, width)):
             raise ValueError("row_norm inputs must be fp16 (rows, width) with a contiguous last dim")
-    y = torch.empty((rows, width), dtype=torch.float16, device=a.device)
+    y = torch.empty((2, rows, width) if mode == 4 else (rows, width), dtype=torch.float16, device=a.device)
     stream = torch.cuda.current_stream(a.device)
     status = capi.load().i4mm_row_norm(
         mode, y.data_ptr(), a.data_ptr(), b.data_ptr() if b is not None else None, c.data_ptr() if c is not None else None,

@@ -309,15 +309,30 @@ class DecoderStack:
         v = fa if mode == 0 else fa + b.float() + c.float() if mode == 1 else fa + rn(b.float()) if mode == 2 else fa * b.float()
         return rn(v).to(torch.float16)
 
+    @classmethod
+    def combine_and_normalise(cls, a: torch.Tensor, b: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+        """(combine(2, a, b), combine(0, of that)): a layer's output and the next layer's normalised input; one launch
+        on CUDA tensors."""
+        if a.is_cuda:
+            from . import ops
+            both = ops.row_norm(4, a, b)
+            return both[0], both[1]
+        h = cls.combine(2, a, b)
+        return h, cls.combine(0, h)
+
     def forward(self, h: torch.Tensor) -> torch.Tensor:
         comb = self.combine
-        for mats in self.layers:
-            q, k, v = self._linear(mats["qkv"], comb(0, h), 3, "qkv")
+        x = comb(0, h)
+        for i, mats in enumerate(self.layers):
+            q, k, v = self._linear(mats["qkv"], x, 3, "qkv")
             t = comb(1, q, k, v)
             (o,) = self._linear(mats["o"], t, 1, "o")
             h = comb(2, h, o)
             gate, up = self._linear(mats["gate_up"], h, 2, "gate_up")
             a = comb(3, gate, up)
             (d,) = self._linear(mats["down"], a, 1, "down")
-            h = comb(2, h, d)
+            if i + 1 < len(self.layers):
+                h, x = self.combine_and_normalise(h, d)
+            else:
+                h = comb(2, h, d)
         return h

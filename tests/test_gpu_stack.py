@@ -18,7 +18,7 @@ def rn(f):
     return f * torch.rsqrt(f.pow(2).mean(dim=-1, keepdim=True) + 1e-6)
 
 
-@pytest.mark.parametrize("rows,width", [(1, 5120), (3, 13824), (70, 256)])
+@pytest.mark.parametrize("rows,width", [(1, 5120), (3, 13824), (70, 256), (2, 14336), (2, 14338), (1, 27648)])
 def test_row_norm_modes_match_the_fp32_expression(rows, width):
     g = torch.Generator().manual_seed(rows * 7 + width)
     buf = (torch.randn((rows, 3 * width), generator=g) * 3).to(torch.float16).cuda()
@@ -32,6 +32,10 @@ def test_row_norm_modes_match_the_fp32_expression(rows, width):
         # fp32 math on both sides, different summation order inside the row reduction: within 1 fp16 ulp
         ulp = oracle.fp16_ulp_distance(y.cpu().numpy(), w.to(torch.float16).cpu().numpy())
         assert ulp.max() <= 1, f"mode {mode}: {ulp.max()} ulp"
+    # mode 4 = mode 2 and mode 0 of its result from one launch: the same bits as the two launches
+    both = ops.row_norm(4, a, b)
+    assert both.shape == (2, rows, width)
+    assert torch.equal(both[0], got[2]) and torch.equal(both[1], ops.row_norm(0, got[2]))
 
 
 def test_stack_linears_match_the_oracle_on_the_inputs_they_received():
