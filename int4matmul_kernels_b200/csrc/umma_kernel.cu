@@ -64,6 +64,12 @@ struct UmmaParams {
     GroupDiv gdiv;
 };
 
+// (mask & a) | (~mask & b)
+__device__ __forceinline__ uint32_t bit_select(uint32_t mask, uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("lop3.b32 %0, %1, %2, %3, 0xCA;" : "=r"(d) : "r"(mask), "r"(a), "r"(b));
+    return d;
+}
 __device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t b, uint32_t c) {
     uint32_t d;
     asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
@@ -97,19 +103,23 @@ constexpr uint32_t MUL_16_64 = 0x24002C00u, BASE_16_64 = 0xCC00D400u;    // (x16
 constexpr uint32_t MUL_1_8 = 0x30003C00u, BASE_1_8 = 0xD800E400u;        // (x1, x8):  int3 field pairs
 constexpr uint32_t MUL_1_1 = 0x3C003C00u, BASE_1_1 = 0xE400E400u;        // (x1, x1): sparse int4 through bytes
 
-// 16-entry table for the sparse expansion (see sparse decode): x = PRMT selector | (4 * popc) << 16, y / z = pair masks
-__device__ __forceinline__ uint4 sparse_lut_entry(int mn) {
-    uint32_t sel = 0, rank = 0, pm[2] = {0, 0};
-    for (int j = 0; j < 4; ++j) {
-        if (mn & (1 << j)) {
-            sel |= rank << (4 * j);
-            pm[j >> 1] |= 0xFFFFu << (16 * (j & 1));
+// 256-entry table for the sparse expansion, indexed by one byte of the keep-mask (8 positions; see the sparse decode).
+// The next 8 kept nibbles are spread over the 8 bytes of a register pair (even nibbles, odd nibbles); for position p
+// with rank r among the kept ones the PRMT selector names byte r / 2 of the even or (4 +) of the odd register.
+//   x = selector of positions 0..3 | (4 * popcount) << 16 (PRMT reads only the low 16 bits of its selector)
+//   y = selector of positions 4..7      z, w = 0xFF in the bytes of the kept positions 0..3, 4..7
+constexpr int kSparseLutEntries = 256;
+__device__ __forceinline__ uint4 sparse_lut_entry(int mb) {
+    uint32_t sel[2] = {0, 0}, keep[2] = {0, 0}, rank = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        if (mb & (1 << j)) {
+            sel[j >> 2] |= ((rank >> 1) + 4u * (rank & 1u)) << (4 * (j & 3));
+            keep[j >> 2] |= 0xFFu << (8 * (j & 3));
             ++rank;
-        } else {
-            sel |= 4u << (4 * j);
         }
     }
-    return make_uint4(sel | ((4 * rank) << 16), pm[0], pm[1], 0);
+    return make_uint4(sel[0] | ((4 * rank) << 16), sel[1], keep[0], keep[1]);
 }
 
 // ---- formats: one 64-k part of one column -> 32 registers of fp16 pairs -----------------------------------------
@@ -216,23 +226,32 @@ struct UFormat<4, true, PERM> {
         const uint32_t off = hsub2_u(BASE_1_1, c.z2);
 #pragma unroll
         for (int blk = 0; blk < 2; ++blk) {
+            // a 32-block of this column: the 64-bit word of its 16 kept nibbles (in increasing k) and its keep-mask
             uint32_t lo = ptx::lds32(wbase + (2 * blk) * 512), hi = ptx::lds32(wbase + (2 * blk + 1) * 512);
             const uint32_t m = ptx::lds32(mbase + blk * 512);
 #pragma unroll
-            for (int chn = 0; chn < 8; ++chn) {
-                const uint4 e = lut[(m >> (4 * chn)) & 0xFu];
-                uint32_t v = lo & 0xFFFFu;                       // next 4 compacted nibbles
-                v = (v | (v << 8)) & 0x00FF00FFu;
-                v = (v | (v << 4)) & 0x0F0F0F0Fu;                // one nibble per byte
-                const uint32_t dep = prmt(v, c.zb, e.x & 0xFFFFu);   // kept -> its nibble, dropped -> zero-point byte
-                uint32_t a = finish<4, MODE>(prmt(dep, 0x64646464u, 0x5140), MUL_1_1, BASE_1_1, off, c);
-                uint32_t b = finish<4, MODE>(prmt(dep, 0x64646464u, 0x7362), MUL_1_1, BASE_1_1, off, c);
-                if (MODE != MODE_FAST) { a &= e.y; b &= e.z; }   // exact zeros at dropped positions
-                A[16 * blk + 2 * chn] = a;
-                A[16 * blk + 2 * chn + 1] = b;
-                const uint32_t sh = e.x >> 16;
-                lo = __funnelshift_r(lo, hi, sh);
-                hi >>= sh;
+            for (int byte = 0; byte < 4; ++byte) {               // 8 positions per step
+                const uint4 e = lut[(m >> (8 * byte)) & 0xFFu];
+                const uint32_t even = lo & 0x0F0F0F0Fu;          // kept nibbles 0, 2, 4, 6 of the next eight, one per byte
+                const uint32_t odd = (lo >> 4) & 0x0F0F0F0Fu;    // kept nibbles 1, 3, 5, 7
+                uint32_t d[2] = {prmt(even, odd, e.x), prmt(even, odd, e.y)};   // positions 0..3, 4..7 as bytes
+                const uint32_t keep[2] = {e.z, e.w};
+#pragma unroll
+                for (int q4 = 0; q4 < 2; ++q4) {
+                    // fast mode: a dropped position gets the (integer) zero-point as its nibble, so it decodes to +0
+                    if (MODE == MODE_FAST) d[q4] = bit_select(keep[q4], d[q4], c.zb);
+                    uint32_t a = finish<4, MODE>(prmt(d[q4], 0x64646464u, 0x5140), MUL_1_1, BASE_1_1, off, c);
+                    uint32_t b = finish<4, MODE>(prmt(d[q4], 0x64646464u, 0x7362), MUL_1_1, BASE_1_1, off, c);
+                    if (MODE != MODE_FAST) {                     // exact zeros at dropped positions
+                        a &= prmt(keep[q4], keep[q4], 0x1100);
+                        b &= prmt(keep[q4], keep[q4], 0x3322);
+                    }
+                    A[16 * blk + 4 * byte + 2 * q4] = a;
+                    A[16 * blk + 4 * byte + 2 * q4 + 1] = b;
+                }
+                const uint32_t sh = e.x >> 16;                   // 4 bits per kept position, up to 32
+                lo = __funnelshift_rc(lo, hi, sh);
+                hi = __funnelshift_rc(hi, 0u, sh);
             }
         }
     }
@@ -362,7 +381,7 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p, const __h
     constexpr int kABStages = ABStages<NT, PAIR>::value;
     extern __shared__ __align__(1024) unsigned char smem[];      // [B ring (1024-aligned tiles)][W ring]
     __shared__ __align__(8) Barriers bars;
-    __shared__ uint4 lut[16];
+    __shared__ uint4 lut[SPARSE ? kSparseLutEntries : 1];
     __shared__ uint32_t tmem_base_smem;
     __shared__ volatile int s_abort;     // set by a warp that gives up on the accumulator (the MMA warp before it releases the epilogue
                                          // warps for the last time; an epilogue warp before its group's next named barrier)
@@ -407,7 +426,7 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p, const __h
             }
             ptx::fence_mbar_init();
         }
-        if (SPARSE && warp == 1 && lane < 16) lut[lane] = sparse_lut_entry(lane);
+        if (SPARSE && warp < 8) lut[warp * 32 + lane] = sparse_lut_entry(warp * 32 + lane);   // (warps 0..7 are dequant warps in every configuration)
         if (warp == kMma) {
             if (PAIR) {
                 ptx::tmem_alloc_pair(ptx::smem_u32(&tmem_base_smem), C::kTmemCols);
