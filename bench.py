@@ -443,16 +443,38 @@ def run_stack(args):
         t = torch.tensor([float(n_bad), 0.0 if gather_ok else 1.0, float(worst_ulp)], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         n_bad, gather_ok, worst_ulp = int(t[0].item()), t[1].item() == 0.0, int(t[2].item())
+    # the whole pass: the output of the timed steps (launched back to back, launches overlapping) must be, bit for bit,
+    # what a pass that synchronises the device after every launch computes
+    def synchronised(fn):
+        def call(*a, **k):
+            y = fn(*a, **k)
+            torch.cuda.synchronize()
+            return y
+        return call
+    timed_out = out.clone()
+    patched = ("combine", "combine_and_normalise", "_linear")
+    for attr in patched:
+        setattr(stack, attr, synchronised(getattr(stack, attr)))
+    try:
+        pass_ok = bool(torch.equal(stack.forward(h0), timed_out))
+    finally:
+        for attr in patched:
+            delattr(stack, attr)
+    if world > 1:
+        t = torch.tensor([0.0 if pass_ok else 1.0], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        pass_ok = t.item() == 0.0
     from int4matmul_kernels_b200 import ops as _ops
     status_ok = True
     try:
         _ops.check_device_status()
     except Exception:
         status_ok = False
-    parity = dict(checked=True, ok=(n_bad == 0 and gather_ok and status_ok), out_of_tolerance=n_bad, max_ulp=worst_ulp,
+    parity = dict(checked=True, ok=(n_bad == 0 and gather_ok and status_ok and pass_ok), out_of_tolerance=n_bad, max_ulp=worst_ulp,
                   elements_per_rank=n_el, frac_bit_identical=exact, gathered_identical_on_all_ranks=gather_ok, ranks=world,
-                  device_status_ok=status_ok,
-                  against="CPU oracle on sampled columns of layer 0's q|k|v product of every rank's shard; gathered buffers compared across ranks")
+                  device_status_ok=status_ok, timed_pass_equals_synchronised_pass=pass_ok,
+                  against="CPU oracle on sampled columns of layer 0's q|k|v product of every rank's shard; gathered buffers compared "
+                          "across ranks; the timed pass's output bit-equal to a pass with a device synchronisation after every launch")
 
     peaks = measured_peaks()
     peak = peaks["hbm"] if kind == "hbm" else peaks["tf_sustained"]

@@ -15,6 +15,11 @@ namespace i4mm {
 
 namespace {
 
+// No pointer of these kernels is __restrict__: they are launched with programmatic stream serialization and may start
+// while the kernel that writes their inputs is still running.  A restrict-qualified input promises the compiler that
+// nothing else writes that memory during the kernel, which lets it move loads above griddepcontrol.wait (observed: the
+// modes with an inner norm read the multiply's output before it was complete).
+
 __device__ __forceinline__ float block_sum(float v, float* red) {
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
     const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
@@ -27,8 +32,8 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 }
 
 template <int MODE>
-__global__ void __launch_bounds__(256) rownorm_kernel(__half* __restrict__ y, const __half* __restrict__ a,
-                                                      const __half* __restrict__ b, const __half* __restrict__ c,
+__global__ void __launch_bounds__(256) rownorm_kernel(__half* y, const __half* a,
+                                                      const __half* b, const __half* c,
                                                       int width, long long sa, long long sb, long long sc) {
     __shared__ float red[32];
     // Launched with programmatic stream serialization: the kernel after this one may be scheduled at once (a multiply
@@ -79,8 +84,8 @@ constexpr int kCachedPer = 14;                                     // fp16 pairs
 constexpr int kCachedWidth = 2 * kCachedThreads * kCachedPer;      // 14336
 
 template <int MODE>
-__global__ void __launch_bounds__(kCachedThreads) rownorm_cached_kernel(__half* __restrict__ y, const __half* __restrict__ a,
-                                                                        const __half* __restrict__ b, const __half* __restrict__ c,
+__global__ void __launch_bounds__(kCachedThreads) rownorm_cached_kernel(__half* y, const __half* a,
+                                                                        const __half* b, const __half* c,
                                                                         int width, long long sa, long long sb, long long sc,
                                                                         long long second_output) {
     __shared__ float red[32];

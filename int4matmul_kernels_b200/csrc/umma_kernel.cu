@@ -362,7 +362,7 @@ struct TensorMaps {
 // PERM (up to 8 rows of dense int4 only): the cheaper k order of UFormat, with the activations reordered to match.
 template <int BITS, bool SPARSE, int NT, bool PAIR, bool PERM = false>
 __global__ void __launch_bounds__(Cfg<NT, PAIR>::kThreads, Cfg<NT, PAIR>::kMinBlocks)
-umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p, const __half* __restrict__ x) {
+umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p, const __half* x) {
     using C = Cfg<NT, PAIR>;
     using F = UFormat<BITS, SPARSE, PERM>;
     static_assert(!PERM || (C::kStream && F::kPermutedK), "the permuted k order is for dense int4 weight streaming");
@@ -1116,7 +1116,9 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p, const __h
 
 // Sums the K parts written by umma_kernel (fp32, (part, row, S)) in part order, rounds once to fp16, and puts the
 // scratch back to all-zero (the split-K reduction of the few-row shapes relies on that).  8 columns per thread.
-__global__ void kparts_reduce_kernel(float* __restrict__ parts, const OutMap om, int rows, int S, int kparts) {
+// (no __restrict__ here or on umma_kernel's activations: both kernels may start while the kernel that writes what they
+// read is still running, and a restrict-qualified pointer would allow the compiler to load above griddepcontrol.wait)
+__global__ void kparts_reduce_kernel(float* parts, const OutMap om, int rows, int S, int kparts) {
     // (launched with programmatic stream serialization: the next kernel may be scheduled at once, this one touches
     // nothing before the kernel that wrote the parts has completed)
     ptx::grid_launch_dependents();

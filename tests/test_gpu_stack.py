@@ -38,6 +38,86 @@ def test_row_norm_modes_match_the_fp32_expression(rows, width):
     assert torch.equal(both[0], got[2]) and torch.equal(both[1], ops.row_norm(0, got[2]))
 
 
+@pytest.mark.parametrize("rows", [5, 40, 200])
+def test_row_norm_launched_behind_a_multiply_reads_its_finished_output(rows):
+    """The glue kernels are launched so that they may start while the kernel before them is still running (and so is
+    the reduce kernel of a multiply whose K range was cut into parts); what they read must be that kernel's finished
+    output.  Chains launched back to back without a synchronisation against the same chains with one, at the sizes of
+    the 13B-class stack (a 13824 -> 5120 multiply: K parts at 40 rows, CTA pairs at 200), ordinary launches and
+    launches that may overlap."""
+    cfg = sharding.StackConfig(hidden=5120, mlp=13824, layers=1, bits=4, group_size=64)
+    w = sharding.synthetic_stack_matrix(cfg, 0, "down", 13824, 5120, torch.device("cuda"))
+    g = torch.Generator().manual_seed(rows)
+    xs = [torch.randn((rows, w.n), generator=g).to(torch.float16).cuda() for _ in range(3)]
+    h = torch.randn((rows, w.s), generator=g).to(torch.float16).cuda()
+
+    def glue(mode, d):
+        return ops.row_norm(mode, d) if mode == 0 else ops.row_norm(mode, d, h, d) if mode == 1 else ops.row_norm(mode, h, d)
+
+    for static in (False, True):
+        for mode in range(5):
+            refs = []
+            for x in xs:
+                d = sharding.cuda_multiply(w, x)
+                torch.cuda.synchronize()
+                refs.append(glue(mode, d))
+                torch.cuda.synchronize()
+            ops.set_static_weights(static)
+            try:
+                outs = [glue(mode, sharding.cuda_multiply(w, xs[i % 3])) for i in range(24)]
+                torch.cuda.synchronize()
+            finally:
+                ops.set_static_weights(False)
+            bad = [i for i, o in enumerate(outs) if not torch.equal(o, refs[i % 3])]
+            assert not bad, f"rows {rows} mode {mode} static {static}: launches {bad} differ from the synchronised ones"
+    ops.check_device_status()
+
+
+class _SynchronisedStack(sharding.DecoderStack):
+    """The stack with a device synchronisation after every launch: the reference for what a pass must compute."""
+
+    @staticmethod
+    def combine(mode, a, b=None, c=None):
+        y = sharding.DecoderStack.combine(mode, a, b, c)
+        torch.cuda.synchronize()
+        return y
+
+    @classmethod
+    def combine_and_normalise(cls, a, b):
+        y = sharding.DecoderStack.combine_and_normalise(a, b)
+        torch.cuda.synchronize()
+        return y
+
+
+@pytest.mark.parametrize("rows", [1, 5, 40, 200])
+def test_stack_pass_at_full_width_is_the_same_with_and_without_synchronisation(rows):
+    """Two layers at the 13B-class widths: passes launched back to back (ordinary launches, then launches that may
+    overlap) must give the bits of a pass that synchronises after every launch."""
+    cfg = sharding.StackConfig(hidden=5120, mlp=13824, layers=2, bits=4, group_size=64)
+
+    def synced_multiply(w, x):
+        y = sharding.cuda_multiply(w, x)
+        torch.cuda.synchronize()
+        return y
+
+    plain = sharding.DecoderStack(cfg, 0, 1, torch.device("cuda"))
+    synced = _SynchronisedStack(cfg, 0, 1, torch.device("cuda"), multiply=synced_multiply)
+    synced.layers = plain.layers                                   # the same weights
+    h = torch.randn((rows, cfg.hidden), generator=torch.Generator().manual_seed(rows)).to(torch.float16).cuda()
+    want = synced.forward(h)
+    torch.cuda.synchronize()
+    for static in (False, True):
+        ops.set_static_weights(static)
+        try:
+            outs = [plain.forward(h) for _ in range(6)]
+            torch.cuda.synchronize()
+        finally:
+            ops.set_static_weights(False)
+        bad = [i for i, o in enumerate(outs) if not torch.equal(o, want)]
+        assert not bad, f"rows {rows} static {static}: passes {bad} differ from the synchronised pass"
+    ops.check_device_status()
+
+
 def test_stack_linears_match_the_oracle_on_the_inputs_they_received():
     cfg = sharding.StackConfig(hidden=256, mlp=512, layers=2, bits=4, group_size=64)
     calls = []
