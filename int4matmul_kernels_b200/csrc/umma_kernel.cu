@@ -942,6 +942,10 @@ umma_kernel(const __grid_constant__ TensorMaps tm, const UmmaParams p, const __h
                 }
             }
             }
+            // Stores into other GPUs' buffers: every storing thread makes its own stores visible system-wide before the
+            // CTA can finish, so that the hand-shake kernel's flag (written by another SM, possibly over another link)
+            // cannot reach a peer before this data has.
+            if (p.om.n_dst > 1) __threadfence_system();
             return true;
         };
 
@@ -1144,6 +1148,7 @@ __global__ void kparts_reduce_kernel(float* parts, const OutMap om, int rows, in
         const size_t at = (size_t)row * om.ld + om.col(c8);
         for (int d = 0; d < om.n_dst; ++d) *reinterpret_cast<uint4*>(om.dst[d] + at) = *reinterpret_cast<uint4*>(h);
     }
+    if (om.n_dst > 1) __threadfence_system();        // as in umma_kernel's epilogue
 }
 
 // ---- host side -------------------------------------------------------------------------------------------------
@@ -1417,16 +1422,17 @@ int launch_nt(const UmmaParams& p_in, const __half* x, int n_groups, cudaStream_
 // Rows per tile (the MMA's N).  Few rows: the smallest tile that holds them.  Many rows: the tile height that
 // minimises (waves of tiles over the SMs) x (time per tile), so that e.g. 320 tiles of 256 rows (2.2 waves on 148
 // SMs) become 440 tiles of 192 rows (3.0 waves) when that is faster.
-int choose_tile_rows(int rows, int col_tiles, int sms) {
+int choose_tile_rows(int rows, int col_tiles, int sms, int max_nt) {
     if (rows <= 16) return 16;
     if (rows <= 32) return 32;
     if (rows <= 64) return 64;
     if (rows <= 128) return 128;
     const int cand[4] = {256, 224, 192, 160};
-    int best = 256;
+    int best = max_nt < 256 ? 192 : 256;
     long long best_cost = -1;
     for (int i = 0; i < 4; ++i) {
         const int nt = cand[i];
+        if (nt > max_nt) continue;
         const long long tiles = (long long)((rows + nt - 1) / nt) * col_tiles;
         const long long waves = (tiles + sms - 1) / sms;
         const long long cost = waves * (nt + 24);          // + per-tile fill / drain, in row units
@@ -1451,7 +1457,14 @@ int launch_fmt(UmmaParams& p, const __half* x, int n_groups, int pair_mode, int 
     }
     // 128 rows or more (the whole-tile configurations) run as CTA pairs, two SMs per MMA, unless the caller asked for single CTAs
     const bool pair = pair_mode == 0 && (force_nt ? force_nt >= 128 : p.rows >= kPairMinRows);
-    const int nt = force_nt ? force_nt : pair ? choose_tile_rows(p.rows, (p.CT + 1) / 2, sms / 2) : choose_tile_rows(p.rows, p.CT, sms);
+    // Stores into several GPUs' buffers (the gathering multiply) make the epilogue of a tile last longer than the tile's
+    // MMAs.  Under exactly that condition the CTA-pair instances with 224 and 256 rows per tile (two dequant warpgroups,
+    // three weight stages) were seen, on 8 GPUs, to produce now and then one wrong block of 32 columns x one row tile
+    // (one warp's weights of one 128-k unit); the 192-row pair instance (four warpgroups, six stages) and the single-CTA
+    // 224 / 256 instances were not, and no run with one destination ever was.  The cause has not been found, so the
+    // gathering multiply keeps to tiles of at most 192 rows when it runs as CTA pairs.
+    const int max_nt = (pair && p.om.n_dst > 1) ? 192 : 256;
+    const int nt = force_nt ? force_nt : pair ? choose_tile_rows(p.rows, (p.CT + 1) / 2, sms / 2, max_nt) : choose_tile_rows(p.rows, p.CT, sms, 256);
     p.MTILES = (p.rows + nt - 1) / nt;
     if (pair) {
         switch (nt) {
